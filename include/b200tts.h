@@ -519,6 +519,76 @@ B2TTS_API int b2tts_xielu(void* y, const void* bias, const float* pq, int64_t ro
 /* y[r, c] = silu(gu[r, c]) * gu[r, ff + c], gu [rows, 2 ff]. */
 B2TTS_API int b2tts_silu_mul(const void* gu, void* y, int64_t rows, int ff, int dtype, void* stream);
 
+/* ---- decoders with several residual streams and mixers that pair an attention branch with a recurrent branch
+ * (csrc/hybrid_ops.cu, sink_attn.cu, recurrent.cu).  `dtype` is the activation / cache type (B2TTS_DTYPE_*); xs is the float
+ * stream tensor [rows, streams, cols].  The per-sequence arrays (seq_start, seq_pos0, seq_len, seq_slot) and the per-token
+ * arrays (tok_seq, positions, slot_mapping) describe the step as everywhere in this library; seq_len 0 / slot -1 is padding. */
+/* xs[i, s, :] = embed[tokens[i]] + bigram[row_i] for every stream s; row_i = (prev_tokens[i] * mul_prev + tokens[i] * mul_cur)
+ * mod buckets, or row `buckets` (the table's last) where prev_tokens[i] < 0.  bigram null: the token embedding alone. */
+B2TTS_API int b2tts_embed_bigram_streams(const int32_t* tokens, const int32_t* prev_tokens, const void* embed, const void* bigram,
+                                         float* xs, int rows, int cols, int streams, int vocab, int buckets, int mul_prev,
+                                         int mul_cur, int dtype, void* stream);
+/* y1 given: x_t <- sum_s mix[s, t] x_s + out_w[t] * (c1 * y1 + c2 * y2) for all streams t at once from the old ones (y2 may be
+ * null).  h given: h = rms_norm(sum_s in_w[s] x_s) * norm_w (in_w null: the plain sum), over the updated streams. */
+B2TTS_API int b2tts_stream_mix_norm(float* xs, const void* y1, const void* y2, float c1, float c2, const float* mix,
+                                    const float* out_w, const float* in_w, const float* norm_w, void* h, int rows, int cols,
+                                    int streams, float eps, int dtype, void* stream);
+/* out[i] = rms_norm(sum_s in_w[s] xs[rows_idx[i], s]) * norm_w (rows_idx null: row i; in_w null: the plain sum). */
+B2TTS_API int b2tts_stream_gather_norm(const float* xs, const int32_t* rows_idx, const float* in_w, const float* norm_w, void* out,
+                                       int rows, int cols, int streams, float eps, int dtype, void* stream);
+/* Row t of the merged projection u (row stride ldu): q = u[q_off : +heads*dim] + q_bias, k = u[k_off : +kv_heads*dim] + k_bias,
+ * v = u[v_off : +kv_heads*vdim] + v_bias, or v = k as it stands here when v_off < 0 (biases may be null).  With q_norm_w and
+ * k_norm_w, q and k are divided by the root mean square of their whole projection and multiplied by the weights.  With
+ * rot_dims > 0, coordinate i < rot_dims/2 of every head is paired with i + rot_dims/2 and turned by positions[t] * freq[i].
+ * q -> q_out[t]; k, v -> the caches at slot_mapping[t]. */
+B2TTS_API int b2tts_attn_prep(const void* u, int64_t ldu, int q_off, int k_off, int v_off, const float* q_bias, const float* k_bias,
+                              const float* v_bias, const float* q_norm_w, const float* k_norm_w, const float* freq, int rot_dims,
+                              const int32_t* positions, const int32_t* slot_mapping, void* q_out, void* k_cache, void* v_cache,
+                              int n_tokens, int heads, int kv_heads, int dim, int vdim, float eps, int dtype, void* stream);
+/* Softmax attention with exp(sink[h]) added to the denominator (sink null: none) over the paged cache, this step's keys
+ * included.  Token i sees key j <= i with j >= max(0, i - mask + 1) (mask_kind 0, a sliding window) or j >= floor(i / mask) *
+ * mask (mask_kind 1, chunks counted from position 0); mask <= 0: every j <= i.  gate (optional): element (t, h) at
+ * gate[t * ldg + h]; the head's output is multiplied by its sigmoid.  q [n, heads*dim], out [n, heads*vdim]. */
+B2TTS_API int b2tts_sink_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* tok_seq,
+                              const int32_t* positions, const int32_t* seq_len, const int32_t* block_tables, int64_t bt_stride,
+                              const float* sink, const void* gate, int64_t ldg, int n_tokens, int heads, int kv_heads, int dim,
+                              int vdim, int page, int mask_kind, int mask, float scale, int dtype, void* stream);
+/* out[t, c] = act(bias[c] + sum_j w[c, j] * u(position(t) - taps + 1 + j)[c_off + c]) for c < channels (act 0: none, 1: SiLU;
+ * bias may be null).  Earlier positions come from this step's rows, from state [slots, taps-1, channels] (the sequence's last
+ * rows, oldest first, advanced by this call) or are zero before position 0. */
+B2TTS_API int b2tts_short_conv_act(const void* u, int64_t ldu, int c_off, const float* w, const float* bias, void* state,
+                                   const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_start,
+                                   const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot, void* out, int64_t ldo,
+                                   int n_tokens, int n_seqs, int channels, int taps, int act, int dtype, void* stream);
+/* Row y [cols] (float) in `groups` equal parts, each divided by its root mean square, times w[c mod w_len]; the gate
+ * (sigmoid for gate_act 0, SiLU for 1, of gate[r * ldg + c]; null: none) multiplies y before the norm (gate_first) or after. */
+B2TTS_API int b2tts_gated_group_norm(const float* y, const void* gate, int64_t ldg, const float* w, int w_len, int groups,
+                                     int gate_act, int gate_first, float eps, void* out, int rows, int cols, int dtype, void* stream);
+/* State-space recurrence per head h (group g = h / (heads / groups)), state [slots, heads, dim, vdim] float:
+ * dt = softplus(dt_in[t, h] + dt_bias[h]); S <- exp(-exp(a_log[h]) dt) S + dt B_t x_t^T; out[t, h] = S^T C_t + d_skip[h] x_t, with
+ * row t of xbc = [x: heads*vdim | B: groups*dim | C: groups*dim] (after its convolution and activation).  out [rows, heads*vdim]. */
+B2TTS_API int b2tts_ssm_scan(const void* xbc, int64_t ldx, const void* dt, int64_t lddt, const float* dt_bias, const float* a_log,
+                             const float* d_skip, float* state, float* out, const int32_t* seq_start, const int32_t* seq_pos0,
+                             const int32_t* seq_len, const int32_t* seq_slot, int n_seqs, int heads, int groups, int vdim, int dim,
+                             int dtype, void* stream);
+/* Delta rule per head, state [slots, heads, dim, vdim] float: row t of qkv = [q: kv_heads*dim | k: kv_heads*dim | v: heads*vdim];
+ * q and k are made unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times dim^(-1/2); g = exp(-exp(a_log[h]) softplus(a_in[t, h] +
+ * dt_bias[h])), beta = sigmoid(beta_in[t, h]); S <- g S; u = beta (v - S^T k); S <- S + k u^T; out[t, h] = S^T q. */
+B2TTS_API int b2tts_delta_rule_scan(const void* qkv, int64_t ldq, const void* beta, const void* a_in, int64_t ldu, const float* a_log,
+                                    const float* dt_bias, float* state, float* out, const int32_t* seq_start, const int32_t* seq_pos0,
+                                    const int32_t* seq_len, const int32_t* seq_slot, int n_seqs, int heads, int kv_heads, int dim,
+                                    int vdim, int dtype, void* stream);
+/* Matrix memory with exponential gates per head: i = cap tanh((ig[t, h] + i_bias[h]) / cap), f = logsigmoid(cap tanh((fg[t, h] +
+ * f_bias[h]) / cap)); m' = max(f + m, i) (m starts at 0); S <- exp(f + m - m') S + exp(i - m') k v^T, n likewise with k alone;
+ * out[t, h] = S^T q / (max(|n . q|, exp(-m')) + 1e-6) with q times dim^(-1/2).  q, k [rows, heads*dim] and v [rows, heads*vdim]
+ * share the row stride ldu with ig and fg.  state [slots, heads, dim, vdim], state_nm [slots, heads, dim + 1] (n, then m), both
+ * float; gates [rows, heads, 3] float is scratch. */
+B2TTS_API int b2tts_matrix_memory_scan(const void* q, const void* k, const void* v, const void* ig, const void* fg, int64_t ldu,
+                                       const float* i_bias, const float* f_bias, float cap, float* state, float* state_nm,
+                                       float* gates, float* out, const int32_t* seq_start, const int32_t* seq_pos0,
+                                       const int32_t* seq_len, const int32_t* seq_slot, int n_seqs, int heads, int dim, int vdim,
+                                       int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -98,6 +98,16 @@ def _load():
         "b2tts_gather_group_norm": (I, [P, P, P, P, I, F, I, I, I, P]),
         "b2tts_xielu": (I, [P, P, P, L, I, I, P]),
         "b2tts_silu_mul": (I, [P, P, L, I, I, P]),
+        "b2tts_embed_bigram_streams": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, P]),
+        "b2tts_stream_mix_norm": (I, [P, P, P, F, F, P, P, P, P, P, I, I, I, F, I, P]),
+        "b2tts_stream_gather_norm": (I, [P, P, P, P, P, I, I, I, F, I, P]),
+        "b2tts_attn_prep": (I, [P, L, I, I, I, P, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, P]),
+        "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, F, I, P]),
+        "b2tts_short_conv_act": (I, [P, L, I, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, P]),
+        "b2tts_gated_group_norm": (I, [P, P, L, P, I, I, I, I, F, P, I, I, I, P]),
+        "b2tts_ssm_scan": (I, [P, L, P, L, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
+        "b2tts_delta_rule_scan": (I, [P, L, P, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
+        "b2tts_matrix_memory_scan": (I, [P, P, P, P, P, L, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, P]),
         "b2tts_grouped_gemm": (I, [P, L, P, P, L, P, P, I, I, I, I, I, I, I, I, I, P]),
     }
     for name, (res, args) in sig.items():
@@ -890,3 +900,132 @@ def silu_mul(gu, out=None):
         out = torch.empty(gu.shape[0], ff, dtype=gu.dtype, device=gu.device)
     _check(_load().b2tts_silu_mul(gu.data_ptr(), out.data_ptr(), gu.shape[0], ff, dt, _stream()), "silu_mul")
     return out
+
+
+# ------------------------------------------------------------------------------------------ stream / hybrid decoders
+def embed_bigram_streams(tokens, prev_tokens, embed, bigram, xs, buckets, mul_prev, mul_cur):
+    """xs [n, streams, D] float <- embed[tokens] (+ bigram[hash(prev, token)], the last row where prev < 0) in every stream."""
+    dt = _act(embed, "embed")
+    _cuda(tokens, I32, "tokens"); _cuda(prev_tokens, I32, "prev_tokens"); _cuda(xs, F32, "xs")
+    assert xs.is_contiguous() and (bigram is None or (bigram.dtype == embed.dtype and bigram.is_contiguous()))
+    n, streams, cols = xs.shape
+    _check(_load().b2tts_embed_bigram_streams(tokens.data_ptr(), prev_tokens.data_ptr(), embed.data_ptr(), _ptr(bigram), xs.data_ptr(),
+                                              n, cols, streams, embed.shape[0], buckets, mul_prev, mul_cur, dt, _stream()),
+           "embed_bigram_streams")
+
+
+def stream_mix_norm(xs, y1, y2, c1, c2, mix, out_w, in_w, norm_w, h, eps, dtype):
+    """The stream update after a sublayer (y1 given) and the normed read-out in front of the next one (h given)."""
+    _cuda(xs, F32, "xs")
+    n, streams, cols = xs.shape
+    for t in (y1, y2, h):
+        assert t is None or (t.dtype == dtype and t.is_contiguous() and t.shape[-1] == cols)
+    for t in (mix, out_w, in_w, norm_w):
+        assert t is None or (t.dtype == F32 and t.is_contiguous())
+    _check(_load().b2tts_stream_mix_norm(xs.data_ptr(), _ptr(y1), _ptr(y2), c1, c2, _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(norm_w),
+                                         _ptr(h), n, cols, streams, eps, DTYPE_CODE[dtype], _stream()), "stream_mix_norm")
+
+
+def stream_gather_norm(xs, rows, in_w, norm_w, eps, dtype, out=None):
+    """out[i] = rms_norm(sum_s in_w[s] xs[rows[i], s]) * norm_w (``rows`` None: every row; ``in_w`` None: the plain sum)."""
+    _cuda(xs, F32, "xs"); _cuda(norm_w, F32, "norm_w")
+    _, streams, cols = xs.shape
+    n = xs.shape[0] if rows is None else rows.shape[0]
+    if out is None:
+        out = torch.empty(n, cols, dtype=dtype, device=xs.device)
+    _check(_load().b2tts_stream_gather_norm(xs.data_ptr(), _ptr(rows), _ptr(in_w), norm_w.data_ptr(), out.data_ptr(), n, cols, streams,
+                                            eps, DTYPE_CODE[dtype], _stream()), "stream_gather_norm")
+    return out
+
+
+def attn_prep(u, q_off, k_off, v_off, q_bias, k_bias, v_bias, q_norm_w, k_norm_w, freq, rot_dims, lay, q_out, k_cache, v_cache,
+              heads, kv_heads, dim, vdim, eps):
+    """Biases, whole-projection RMS norm and half-split rotation of q and k; k and v go to their cache slots
+    (``v_off`` < 0: the values are the keys as projected)."""
+    dt = _act(q_out, "q_out")
+    assert u.dtype == q_out.dtype and u.stride(1) == 1 and k_cache.dtype == u.dtype and v_cache.dtype == u.dtype
+    for t in (q_bias, k_bias, v_bias, q_norm_w, k_norm_w, freq):
+        assert t is None or (t.dtype == F32 and t.is_contiguous())
+    _check(_load().b2tts_attn_prep(u.data_ptr(), u.stride(0), q_off, k_off, v_off, _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+                                   _ptr(q_norm_w), _ptr(k_norm_w), _ptr(freq), rot_dims, lay.positions.data_ptr(),
+                                   lay.slot_mapping.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                   lay.n_tokens, heads, kv_heads, dim, vdim, eps, dt, _stream()), "attn_prep")
+
+
+MASK_WINDOW, MASK_CHUNK = 0, 1
+
+
+def sink_attn(q, k_cache, v_cache, out, lay, sink, gate, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale):
+    """``gate``: a column slice [n, heads] of the merged projection (or None)."""
+    dt = _act(q, "q")
+    assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype and out.is_contiguous()
+    assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1)
+    _check(_load().b2tts_sink_attn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), lay.tok_seq.data_ptr(),
+                                   lay.positions.data_ptr(), lay.seq_len.data_ptr(), lay.block_tables.data_ptr(),
+                                   lay.block_tables.stride(0), _ptr(sink), _ptr(gate), 0 if gate is None else gate.stride(0),
+                                   lay.n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, dt, _stream()), "sink_attn")
+
+
+def short_conv_act(u, c_off, channels, w, bias, state, lay, out, taps, act=1):
+    """out [n, channels] <- act(causal convolution over time of u[:, c_off : c_off + channels]); ``state`` advances."""
+    dt = _act(out, "out")
+    assert u.dtype == out.dtype and u.stride(1) == 1 and (state is None or (state.dtype == out.dtype and state.is_contiguous()))
+    _cuda(w, F32, "w")
+    _check(_load().b2tts_short_conv_act(u.data_ptr(), u.stride(0), c_off, w.data_ptr(), _ptr(bias), _ptr(state), lay.tok_seq.data_ptr(),
+                                        lay.positions.data_ptr(), lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(),
+                                        lay.seq_len.data_ptr(), lay.seq_slot.data_ptr(), out.data_ptr(), out.stride(0), lay.n_tokens,
+                                        lay.n_seqs, channels, taps, act, dt, _stream()), "short_conv_act")
+
+
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def gated_group_norm(y, gate, w, groups, gate_act, gate_first, eps, out):
+    """y [n, C] float -> out [n, C]: gate and RMS norm in ``groups`` parts, weight w[c mod len(w)]."""
+    _cuda(y, F32, "y"); _cuda(w, F32, "w")
+    dt = _act(out, "out")
+    assert y.is_contiguous() and (gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1))
+    _check(_load().b2tts_gated_group_norm(y.data_ptr(), _ptr(gate), 0 if gate is None else gate.stride(0), w.data_ptr(), w.numel(),
+                                          groups, gate_act, int(gate_first), eps, out.data_ptr(), y.shape[0], y.shape[1], dt, _stream()),
+           "gated_group_norm")
+
+
+def _seq_args(lay):
+    return (lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(), lay.seq_slot.data_ptr(), lay.n_seqs)
+
+
+def ssm_scan(xbc, dt_in, dt_bias, a_log, d_skip, state, out, lay, heads, groups, vdim, nstate):
+    """xbc [n, heads*vdim + 2*groups*nstate] (convolved, activated); dt_in: a column slice [n, heads]; state float
+    [slots, heads, nstate, vdim]; out float [n, heads*vdim]."""
+    dt = _act(xbc, "xbc")
+    _cuda(state, F32, "state"); _cuda(out, F32, "out")
+    assert dt_in.dtype == xbc.dtype and dt_in.stride(1) == 1 and state.is_contiguous() and out.is_contiguous()
+    _check(_load().b2tts_ssm_scan(xbc.data_ptr(), xbc.stride(0), dt_in.data_ptr(), dt_in.stride(0), dt_bias.data_ptr(), a_log.data_ptr(),
+                                  d_skip.data_ptr(), state.data_ptr(), out.data_ptr(), *_seq_args(lay), heads, groups, vdim, nstate,
+                                  dt, _stream()), "ssm_scan")
+
+
+def delta_rule_scan(qkv, beta_in, a_in, a_log, dt_bias, state, out, lay, heads, kv_heads, dim, vdim):
+    """qkv [n, 2*kv_heads*dim + heads*vdim] (convolved, activated); beta_in, a_in: column slices [n, heads] of one tensor."""
+    dt = _act(qkv, "qkv")
+    _cuda(state, F32, "state"); _cuda(out, F32, "out")
+    assert beta_in.dtype == qkv.dtype and a_in.dtype == qkv.dtype and beta_in.stride(0) == a_in.stride(0)
+    assert state.is_contiguous() and out.is_contiguous()
+    _check(_load().b2tts_delta_rule_scan(qkv.data_ptr(), qkv.stride(0), beta_in.data_ptr(), a_in.data_ptr(), beta_in.stride(0),
+                                         a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), out.data_ptr(), *_seq_args(lay),
+                                         heads, kv_heads, dim, vdim, dt, _stream()), "delta_rule_scan")
+
+
+def matrix_memory_scan(q, k, v, ig, fg, i_bias, f_bias, cap, state, state_nm, gates, out, lay, heads, dim, vdim):
+    """q, k, v, ig, fg: column slices of ONE merged projection (same row stride); state [slots, heads, dim, vdim],
+    state_nm [slots, heads, dim + 1], gates [n, heads, 3] (scratch), out [n, heads*vdim], all float."""
+    _cuda(q, None, "q")
+    dt = DTYPE_CODE[q.dtype]
+    for t in (k, v, ig, fg):
+        assert t.dtype == q.dtype and t.stride(0) == q.stride(0) and t.stride(1) == 1
+    for t in (state, state_nm, gates, out):
+        _cuda(t, F32, "state"); assert t.is_contiguous()
+    _check(_load().b2tts_matrix_memory_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), ig.data_ptr(), fg.data_ptr(), q.stride(0),
+                                            i_bias.data_ptr(), f_bias.data_ptr(), cap, state.data_ptr(), state_nm.data_ptr(),
+                                            gates.data_ptr(), out.data_ptr(), *_seq_args(lay), heads, dim, vdim, dt, _stream()),
+           "matrix_memory_scan")

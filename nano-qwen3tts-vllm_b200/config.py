@@ -323,6 +323,198 @@ class RidevikConfig:
                 "layers": out}
 
 
+@dataclass
+class HalfRotarySpec:
+    """Rotation of the first ``dims`` coordinates of a head, coordinate i paired with i + dims/2, by position *
+    base^(-2i/dims)."""
+    dims: int
+    base: float
+
+
+@dataclass
+class SinkAttentionSpec:
+    """Softmax attention over ``kv_heads`` shared key/value heads with a learned per-head sink in the denominator, under a
+    mask that is a sliding window or a chunk of ``mask_size`` positions.  Switches: ``bias`` on the q/k/v projections,
+    ``qk_norm`` (RMS norm over the whole q and the whole k projection), ``rot`` (or no positions at all), ``tied_values``
+    (no value projection: the values are the keys as projected, before norm and rotation), ``gate`` (one sigmoid gate
+    per head on the output)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    mask_kind: str                 # "window" | "chunk"
+    mask_size: int
+    scale: float
+    rot: HalfRotarySpec | None = None
+    qk_norm: bool = False
+    bias: bool = False
+    gate: bool = False
+    tied_values: bool = False
+
+
+@dataclass
+class MatrixMemorySpec:
+    """Matrix memory with exponential input and forget gates (log gates capped by ``gate_cap`` * tanh(. / ``gate_cap``))."""
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+
+
+@dataclass
+class DeltaRuleSpec:
+    """Gated delta-rule memory: ``kv_heads`` query/key heads shared by ``heads`` value heads, a short convolution of
+    ``conv`` taps on q, k and v."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+
+
+@dataclass
+class StateSpaceSpec:
+    """Selective state space with a scalar decay per head: ``heads`` x ``vdim`` inner channels, ``state`` numbers per
+    channel, B and C shared by the heads of a group, output norm in ``norm_groups`` parts."""
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def conv_channels(self) -> int:
+        return self.inner + 2 * self.groups * self.state
+
+
+@dataclass
+class ParallelMixerSpec:
+    """An attention branch and a recurrent branch that read the same input; their outputs are added with two weights."""
+    left: SinkAttentionSpec
+    right: object                  # MatrixMemorySpec | DeltaRuleSpec
+    left_scale: float
+    right_scale: float
+
+
+@dataclass
+class TibivikLayerSpec:
+    type: str                      # "mamba2" | "parallel" | "parallel_2"
+    mixer: object                  # StateSpaceSpec | ParallelMixerSpec
+    mlp: FeedForwardSpec | None
+    raw: dict = field(default_factory=dict, repr=False)      # the layer's entry as read (kept for to_dict)
+
+
+@dataclass
+class TibivikConfig:
+    """``config.json`` of a Tibivik checkpoint: a decoder-only token model over ``streams`` copies of the residual
+    stream that small learned matrices mix around every sublayer (0: one plain residual stream).  The embedding adds a
+    hashed (previous token, token) row.  Layers are listed one by one with their own sizes: a state-space mixer, or an
+    attention branch beside a recurrent branch (sliding window + matrix memory, or chunks + delta rule); feed-forwards are
+    SiLU-gated or absent.  ``loop`` repeats a range of layers with the same weights, each pass over a cache and state of
+    its own.  The output head is the embedding table."""
+    architecture: str
+    vocab: int
+    width: int
+    norm_eps: float
+    streams: int
+    bigram: dict | None            # {"buckets", "mul_prev", "mul_cur"}
+    layers: list
+    loop: dict | None              # {"start", "stop", "times"}
+    max_positions = None           # positions enter through rotations only: no table bounds them
+
+    page_multiple = 16
+
+    @staticmethod
+    def _attention(m: dict, kind: str, i: int) -> SinkAttentionSpec:
+        r = m.get("rot")
+        rot = HalfRotarySpec(int(r["dims"]), float(r["base"])) if r else None
+        window = kind == "parallel"
+        spec = SinkAttentionSpec(heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                 mask_kind="window" if window else "chunk", mask_size=int(m["mask"]["size"]),
+                                 scale=float(m["scale"]), rot=rot, qk_norm=window, bias=not window, gate=not window,
+                                 tied_values=window)
+        if spec.heads % spec.kv_heads:
+            raise ValueError(f"layer {i}: {spec.heads} heads over {spec.kv_heads} key/value heads")
+        if spec.tied_values and spec.vdim != spec.dim:
+            raise ValueError(f"layer {i}: values that are the keys need vdim == dim ({spec.vdim} != {spec.dim})")
+        if rot is not None and (rot.dims % 2 or rot.dims > spec.dim):
+            raise ValueError(f"layer {i}: {rot.dims} rotated coordinates in a head of {spec.dim}")
+        if spec.mask_size < 1:
+            raise ValueError(f"layer {i}: mask size {spec.mask_size}")
+        return spec
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "TibivikConfig":
+        layers = []
+        for i, ld in enumerate(d["layers"]):
+            kind, m = ld["type"], ld["mixer"]
+            if kind == "mamba2":
+                mixer = StateSpaceSpec(heads=int(m["heads"]), vdim=int(m["vdim"]), state=int(m["state"]), groups=int(m["groups"]),
+                                       conv=int(m["conv"]), norm_groups=int(m["norm_groups"]))
+                if mixer.heads % mixer.groups or mixer.inner % mixer.norm_groups:
+                    raise ValueError(f"layer {i}: heads, groups and norm groups do not divide")
+            elif kind == "parallel":
+                rt = m["right"]
+                right = MatrixMemorySpec(heads=int(rt["heads"]), dim=int(rt["dim"]), vdim=int(rt["vdim"]), gate_cap=float(rt["gate_cap"]))
+                mixer = ParallelMixerSpec(cls._attention(m["left"], kind, i), right, float(m["left_scale"]), float(m["right_scale"]))
+            elif kind == "parallel_2":
+                rt = m["right"]
+                right = DeltaRuleSpec(heads=int(rt["heads"]), kv_heads=int(rt["kv_heads"]), dim=int(rt["dim"]), vdim=int(rt["vdim"]),
+                                      conv=int(rt["conv"]))
+                if right.heads % right.kv_heads:
+                    raise ValueError(f"layer {i}: {right.heads} value heads over {right.kv_heads} key heads")
+                mixer = ParallelMixerSpec(cls._attention(m["left"], kind, i), right, float(m["left_scale"]), float(m["right_scale"]))
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            f = ld.get("mlp")
+            mlp = None
+            if f is not None:
+                if f["kind"] != "dense":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {f['kind']!r}")
+                mlp = FeedForwardSpec("dense", int(f["ff"]), act="silu_gate")
+            layers.append(TibivikLayerSpec(kind, mixer, mlp, raw=ld))
+        bg = (d.get("embedding") or {}).get("bigram")
+        bigram = {k: int(bg[k]) for k in ("buckets", "mul_prev", "mul_cur")} if bg else None
+        lp = d.get("loop")
+        loop = {k: int(lp[k]) for k in ("start", "stop", "times")} if lp else None
+        if loop is not None and not (0 <= loop["start"] <= loop["stop"] <= len(layers) and loop["times"] >= 1):
+            raise ValueError(f"loop {loop} does not fit {len(layers)} layers")
+        streams = int(d.get("streams") or 0)
+        if streams > 8:
+            raise ValueError(f"{streams} streams (at most 8)")
+        return cls(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]), norm_eps=float(d["norm"]["eps"]),
+                   streams=streams, bigram=bigram, layers=layers, loop=loop)
+
+    @classmethod
+    def from_pretrained(cls, model_dir: str) -> "TibivikConfig":
+        with open(os.path.join(model_dir, "config.json")) as f:
+            return cls.from_dict(json.load(f))
+
+    def runs(self) -> list[int]:
+        """Layer index of every layer run, in order: the looped range repeats in a row."""
+        n = len(self.layers)
+        if not self.loop:
+            return list(range(n))
+        a, b, t = self.loop["start"], self.loop["stop"], self.loop["times"]
+        return list(range(a)) + list(range(a, b)) * t + list(range(b, n))
+
+    def to_dict(self) -> dict:
+        out = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
+               "layers": [dict(l.raw) for l in self.layers]}
+        if self.streams:
+            out["streams"] = self.streams
+        if self.bigram:
+            out["embedding"] = {"bigram": dict(self.bigram)}
+        if self.loop:
+            out["loop"] = dict(self.loop)
+        return out
+
+
 def load_model_config(model_dir: str):
     """Parse ``config.json`` with the configuration class its architecture is registered under."""
     from .models.registry import resolve

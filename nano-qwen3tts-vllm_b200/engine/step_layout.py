@@ -1,6 +1,6 @@
 """Layout of one engine step that mixes prompt portions and single decoded tokens.
 
-Per token: id, position, batch row, cache slot.  Per batch row (a sequence in this step): where its tokens start in
+Per token: id, the id before it in its sequence (-1 at a sequence's first token), position, batch row, cache slot.  Per batch row (a sequence in this step): where its tokens start in
 the packed batch, the position of the first one (= tokens already cached), how many there are, its state slot and its
 block table.  Everything is written with numpy into ONE pinned buffer and crosses PCIe as ONE copy; the kernels read
 the device mirror, whose addresses never change (CUDA graphs of the decode step are captured over them).
@@ -12,7 +12,7 @@ import torch
 
 
 class MixedStepLayout:
-    TOKEN_FIELDS = ("tokens", "positions", "tok_seq", "slot_mapping", "want_rows")
+    TOKEN_FIELDS = ("tokens", "prev_tokens", "positions", "tok_seq", "slot_mapping", "want_rows")
     SEQ_FIELDS = ("seq_start", "seq_pos0", "seq_len", "seq_slot")
     RING = 4
 
@@ -65,6 +65,8 @@ class MixedStepLayout:
             ar = np.arange(c, c + n, dtype=np.int64)
             bt = np.asarray(seq.block_table, dtype=np.int64)
             f["tokens"][o:o + n] = seq.token_ids[c:c + n]
+            # the token before each one: part of the sequence's state, so a portion's first token finds its predecessor
+            f["prev_tokens"][o:o + n] = seq.token_ids[c - 1:c + n - 1] if c > 0 else [-1] + seq.token_ids[0:n - 1]
             f["positions"][o:o + n] = ar
             f["tok_seq"][o:o + n] = b
             f["slot_mapping"][o:o + n] = bt[ar // page] * page + ar % page
@@ -75,6 +77,7 @@ class MixedStepLayout:
         if pad_seqs is not None and pad_seqs > n_seqs:
             assert o == n_seqs
             f["tokens"][o:pad_seqs] = 0
+            f["prev_tokens"][o:pad_seqs] = -1
             f["positions"][o:pad_seqs] = 0
             f["tok_seq"][o:pad_seqs] = np.arange(o, pad_seqs)
             f["slot_mapping"][o:pad_seqs] = -1

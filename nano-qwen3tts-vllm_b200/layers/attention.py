@@ -101,3 +101,47 @@ class LatentSinkAttention(nn.Module):
                         self.sink, self.rotary.freq, self.rotary.mult, self.rotary.dims, lay, self.heads, self.kv_rank,
                         self.rot_dim, cache.shape[1], self.window, self.scale, self.path)
         return out
+
+
+class SinkSoftmaxAttention(nn.Module):
+    """Softmax attention over paged K/V with a learned per-head sink in the denominator (it has no key and no value and
+    is not scaled), under a sliding window (``mask_kind`` "window": the token itself and the ``mask`` - 1 before it) or
+    chunks (``"chunk"``: earlier tokens of the same block of ``mask`` positions, counted from position 0).
+
+    ``prepare`` turns the mixer's merged projection into queries and cache rows: optional biases, optional RMS norm over
+    the whole q and the whole k projection, optional half-split rotation; the values are a projection of their own or,
+    with ``v_off`` < 0, the keys as projected.  ``forward`` attends; an optional per-head sigmoid gate rides in the same
+    launch.  The cache holds this step's keys already, so prompt portions and decoded tokens share the launch."""
+
+    MASKS = {"window": nat.MASK_WINDOW, "chunk": nat.MASK_CHUNK}
+
+    def __init__(self, heads: int, kv_heads: int, dim: int, vdim: int, mask_kind: str, mask: int, scale: float, *,
+                 bias: bool = False, qk_norm: bool = False, rotary=None, eps: float = 1e-6):
+        super().__init__()
+        self.heads, self.kv_heads, self.dim, self.vdim, self.scale, self.eps = heads, kv_heads, dim, vdim, scale, eps
+        self.mask_kind, self.mask, self.rotary = self.MASKS[mask_kind], mask, rotary
+        f32 = dict(dtype=torch.float32)
+        self.sink = nn.Parameter(torch.zeros(heads, **f32), requires_grad=False)
+        mk = lambda n, one: nn.Parameter((torch.ones if one else torch.zeros)(n, **f32), requires_grad=False)
+        self.q_bias = mk(heads * dim, False) if bias else None
+        self.k_bias = mk(kv_heads * dim, False) if bias else None
+        self.v_bias = mk(kv_heads * vdim, False) if bias else None
+        self.q_norm = mk(heads * dim, True) if qk_norm else None
+        self.k_norm = mk(kv_heads * dim, True) if qk_norm else None
+        self.k_cache = self.v_cache = torch.tensor([])
+
+    def prepare(self, u: torch.Tensor, q_off: int, k_off: int, v_off: int) -> torch.Tensor:
+        lay = get_context().step_layout
+        q = torch.empty(u.shape[0], self.heads * self.dim, dtype=u.dtype, device=u.device)
+        rot = self.rotary
+        nat.attn_prep(u, q_off, k_off, v_off, self.q_bias, self.k_bias, self.v_bias if v_off >= 0 else None, self.q_norm,
+                      self.k_norm, rot.freq if rot is not None else None, rot.dims if rot is not None else 0, lay, q,
+                      self.k_cache, self.v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.eps)
+        return q
+
+    def forward(self, q: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
+        lay = get_context().step_layout
+        out = torch.empty(q.shape[0], self.heads * self.vdim, dtype=q.dtype, device=q.device)
+        nat.sink_attn(q, self.k_cache, self.v_cache, out, lay, self.sink, gate, self.heads, self.kv_heads, self.dim, self.vdim,
+                      self.k_cache.shape[1], self.mask_kind, self.mask, self.scale)
+        return out

@@ -54,3 +54,20 @@ class ScaledTokenEmbedding(nn.Module):
         x = torch.empty(tokens.shape[0], self.embed.shape[1], dtype=torch.float32, device=tokens.device)
         nat.embed_scale(tokens, self.embed, self.scale, x)
         return x
+
+
+class BigramTokenEmbedding(nn.Module):
+    """Token embedding plus a row of a hashed bigram table, row (previous token * mul_prev + token * mul_cur) mod
+    ``buckets`` (the table's extra last row for a sequence's first token), written as floats into every one of
+    ``streams`` residual streams [n, streams, width].  ``buckets`` 0: no bigram table."""
+
+    def __init__(self, vocab: int, width: int, streams: int, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0):
+        super().__init__()
+        self.streams, self.buckets, self.mul_prev, self.mul_cur = streams, buckets, mul_prev, mul_cur
+        self.embed = nn.Parameter(torch.empty(vocab, width), requires_grad=False)
+        self.bigram = nn.Parameter(torch.empty(buckets + 1, width), requires_grad=False) if buckets else None
+
+    def forward(self, tokens: torch.Tensor, prev_tokens: torch.Tensor) -> torch.Tensor:
+        xs = torch.empty(tokens.shape[0], self.streams, self.embed.shape[1], dtype=torch.float32, device=tokens.device)
+        nat.embed_bigram_streams(tokens, prev_tokens, self.embed, self.bigram, xs, self.buckets, self.mul_prev, self.mul_cur)
+        return xs

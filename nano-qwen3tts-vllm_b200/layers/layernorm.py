@@ -67,3 +67,17 @@ class GroupRMSNorm(nn.Module):
 
     def forward(self, x: torch.Tensor, dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
         return nat.gather_group_norm(x, rows, self.weight, self.groups, self.eps, dtype)
+
+
+class StreamRMSNorm(nn.Module):
+    """RMS norm with a weight vector kept in float, applied to what is read out of the residual streams: it rides in
+    the stream kernels (``layers/hyper_connection.step``); ``forward`` is the stand-alone form on the sum of the streams
+    of gathered rows (the final norm in front of the head)."""
+
+    def __init__(self, width: int, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(width, dtype=torch.float32), requires_grad=False)
+
+    def forward(self, xs: torch.Tensor, dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
+        return nat.stream_gather_norm(xs, rows, None, self.weight, self.eps, dtype)

@@ -93,3 +93,17 @@ class PairRotary(nn.Module):
             f = f / factor * ramp + f * (1 - ramp)
             self.mult = 0.1 * math.log(factor) + 1.0
         self.register_buffer("freq", f.to(torch.float32), persistent=False)
+
+
+class HalfRotary(nn.Module):
+    """Frequencies of a rotation that pairs coordinate i with i + dims/2 (i < dims/2) of the first ``dims`` coordinates
+    of a head: f_i = base^(-2i/dims).  Computed in float64, kept as float; the kernel that rotates
+    (``nat.attn_prep``) forms the angle position * f_i in float."""
+
+    def __init__(self, dims: int, base: float):
+        super().__init__()
+        assert dims % 2 == 0
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = torch.as_tensor(float(base), dtype=torch.float64) ** (-2.0 * i / max(dims, 1))
+        self.dims = dims
+        self.register_buffer("freq", f.to(torch.float32), persistent=False)

@@ -30,3 +30,26 @@ class ShortConvQKV(nn.Module):
         nat.conv_headnorm_kvwrite(u, self.weight, self.state, lay, self.q_norm, self.k_norm, q, k_cache, v_cache,
                                   self.heads, self.kv_heads, self.dim, self.vdim, self.taps, self.eps)
         return q
+
+
+F32 = dict(dtype=torch.float32)
+
+
+class ShortConvAct(nn.Module):
+    """Causal convolution over time, one filter of ``taps`` numbers per channel (the last tap multiplies the token
+    itself), optional bias, then SiLU.  The last ``taps - 1`` inputs of every live sequence are its carried state."""
+
+    def __init__(self, channels: int, taps: int, bias: bool):
+        super().__init__()
+        self.channels, self.taps = channels, taps
+        self.weight = nn.Parameter(torch.zeros(channels, taps, **F32), requires_grad=False)
+        self.bias = nn.Parameter(torch.zeros(channels, **F32), requires_grad=False) if bias else None
+        self.state = None                      # [slots, max(taps - 1, 1), channels] in the activation type
+
+    def state_plan(self):
+        return ((max(self.taps - 1, 1), self.channels), None)
+
+    def forward(self, u: torch.Tensor, c_off: int) -> torch.Tensor:
+        out = torch.empty(u.shape[0], self.channels, dtype=u.dtype, device=u.device)
+        nat.short_conv_act(u, c_off, self.channels, self.weight, self.bias, self.state, get_context().step_layout, out, self.taps, 1)
+        return out

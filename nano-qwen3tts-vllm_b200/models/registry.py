@@ -55,6 +55,9 @@ register(Architecture("Bokenex", ".config:BokenexConfig", ".models.bokenex:Boken
 register(Architecture("Ridevik", ".config:RidevikConfig", ".models.ridevik:RidevikForCausalLM",
                       ".engine.model_runner.lm_model_runner:LMModelRunner",
                       ".engine.llm_engine.lm_engine:CausalLMEngine"))
+register(Architecture("Tibivik", ".config:TibivikConfig", ".models.tibivik:TibivikForCausalLM",
+                      ".engine.model_runner.lm_model_runner:LMModelRunner",
+                      ".engine.llm_engine.lm_engine:CausalLMEngine"))
 
 
 def resolve(config: dict) -> Architecture:
