@@ -254,3 +254,116 @@ def forward(sd: dict, config: dict, tokens, dtype=torch.float64, layers_out: lis
         if layers_out is not None:
             layers_out.append(sum(xs))
     return rms_norm(sum(xs), sd["final.norm"], eps) @ sd["embed"].T
+
+
+# ------------------------------------------------------------------------------------------------ random models for tests
+def random_config(*, width=40, vocab=53, streams=2, bigram=(31, 5, 3), types=("mamba2", "parallel_2", "parallel"), loop=None,
+                  ff=(24, None, 56), eps=1e-5, ssm=None, window=None, chunk=None, memory=None, delta=None,
+                  scales=(0.7, 1.2)) -> dict:
+    """A small configuration; ``ssm`` / ``window`` / ``chunk`` / ``memory`` / ``delta`` override the default sizes of
+    the state-space mixer, the two attention branches and the two recurrent branches; ``ff`` cycles over the layers
+    (None: no feed-forward); ``bigram`` = (buckets, mul_prev, mul_cur) or None; ``streams`` 0: one plain residual."""
+    s = dict(heads=3, vdim=8, state=6, groups=1, conv=3, norm_groups=1)
+    s.update(ssm or {})
+    w = dict(heads=4, kv_heads=2, dim=12, vdim=12, mask={"size": 7}, scale=0.3, rot={"dims": 8, "base": 100.0})
+    w.update(window or {})
+    c = dict(heads=3, kv_heads=1, dim=10, vdim=6, mask={"size": 5}, scale=0.25)
+    c.update(chunk or {})
+    m = dict(heads=2, dim=6, vdim=10, gate_cap=8.0)
+    m.update(memory or {})
+    d = dict(heads=4, kv_heads=2, dim=6, vdim=5, conv=4)
+    d.update(delta or {})
+    layers = []
+    for i, kind in enumerate(types):
+        f = ff[i % len(ff)]
+        mlp = {"kind": "dense", "ff": f} if f else None
+        if kind == "mamba2":
+            mixer = dict(s)
+        elif kind == "parallel":
+            mixer = {"left": dict(w), "right": dict(m), "left_scale": scales[0], "right_scale": scales[1]}
+        else:
+            mixer = {"left": dict(c), "right": dict(d), "left_scale": scales[0], "right_scale": scales[1]}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    cfg = {"architecture": "Tibivik", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if streams:
+        cfg["streams"] = streams
+    if bigram:
+        cfg["embedding"] = {"bigram": {"buckets": bigram[0], "mul_prev": bigram[1], "mul_cur": bigram[2]}}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return cfg
+
+
+def random_weights(config: dict, seed: int = 0) -> dict:
+    """Random tensors (rounded to bfloat16, as a checkpoint stores them) under the checkpoint's names."""
+    g = torch.Generator().manual_seed(seed)
+    D = config["width"]
+    sd = {}
+
+    def put(name, *shape, std=1.0, mean=0.0):
+        sd[name] = (mean + std * torch.randn(shape, generator=g)).to(torch.bfloat16).to(torch.float32)
+
+    put("embed", config["vocab"], D)
+    bg = config.get("embedding", {}).get("bigram")
+    if bg:
+        put("bigram", bg["buckets"] + 1, D, std=0.5)
+    put("final.norm", D, mean=1.0, std=0.1)
+    s = config.get("streams")
+    for i, spec in enumerate(config["layers"]):
+        p, m = f"l{i}.", spec["mixer"]
+        subs = [1] + ([2] if spec.get("mlp") else [])
+        for q in subs:
+            put(f"{p}norm{q}", D, mean=1.0, std=0.1)
+            if s:
+                put(f"{p}hc{q}.in", s, mean=0.7, std=0.3)
+                put(f"{p}hc{q}.out", s, mean=0.8, std=0.3)
+                sd[f"{p}hc{q}.mix"] = (torch.eye(s) + 0.25 * torch.randn(s, s, generator=g)).to(torch.bfloat16).to(torch.float32)
+        if spec.get("mlp"):
+            f = spec["mlp"]["ff"]
+            put(p + "mlp.gate", f, D, std=D ** -0.5)
+            put(p + "mlp.up", f, D, std=D ** -0.5)
+            put(p + "mlp.down", D, f, std=f ** -0.5)
+        if spec["type"] == "mamba2":
+            inner, ch = m["heads"] * m["vdim"], m["heads"] * m["vdim"] + 2 * m["groups"] * m["state"]
+            put(p + "mix.in", inner + ch + m["heads"], D, std=D ** -0.5)
+            put(p + "mix.conv", ch, m["conv"], std=0.5)
+            put(p + "mix.conv.b", ch, std=0.2)
+            put(p + "mix.dt_bias", m["heads"], std=0.5)
+            put(p + "mix.A_log", m["heads"], std=0.5, mean=-0.5)
+            put(p + "mix.D", m["heads"], std=0.5)
+            put(p + "mix.norm", inner, mean=1.0, std=0.1)
+            put(p + "mix.o", D, inner, std=inner ** -0.5)
+            continue
+        l, r = m["left"], m["right"]
+        L, R = p + "mix.left.", p + "mix.right."
+        put(L + "q", l["heads"] * l["dim"], D, std=D ** -0.5)
+        put(L + "k", l["kv_heads"] * l["dim"], D, std=D ** -0.5)
+        put(L + "sink", l["heads"], std=1.0)
+        put(L + "o", D, l["heads"] * l["vdim"], std=(l["heads"] * l["vdim"]) ** -0.5)
+        if spec["type"] == "parallel":
+            put(L + "q.norm", l["heads"] * l["dim"], mean=1.0, std=0.1)
+            put(L + "k.norm", l["kv_heads"] * l["dim"], mean=1.0, std=0.1)
+            hd, hv = r["heads"] * r["dim"], r["heads"] * r["vdim"]
+            for n, rows in (("q", hd), ("k", hd), ("v", hv), ("g", hv), ("i", r["heads"]), ("f", r["heads"])):
+                put(R + n, rows, D, std=D ** -0.5)
+            put(R + "i.b", r["heads"], std=0.5)
+            put(R + "f.b", r["heads"], std=0.5, mean=1.0)
+            put(R + "norm", hv, mean=1.0, std=0.1)
+            put(R + "o", D, hv, std=hv ** -0.5)
+        else:
+            put(L + "v", l["kv_heads"] * l["vdim"], D, std=D ** -0.5)
+            put(L + "g", l["heads"], D, std=D ** -0.5)
+            for n, rows in (("q.b", l["heads"] * l["dim"]), ("k.b", l["kv_heads"] * l["dim"]), ("v.b", l["kv_heads"] * l["vdim"])):
+                put(L + n, rows, std=0.3)
+            gd, hv = r["kv_heads"] * r["dim"], r["heads"] * r["vdim"]
+            for n, rows in (("q", gd), ("k", gd), ("v", hv)):
+                put(R + n, rows, D, std=D ** -0.5)
+                put(R + n + ".conv", rows, r["conv"], std=0.5)
+            put(R + "g", hv, D, std=D ** -0.5)
+            put(R + "b", r["heads"], D, std=D ** -0.5)
+            put(R + "a", r["heads"], D, std=D ** -0.5)
+            put(R + "A_log", r["heads"], std=0.5, mean=-0.5)
+            put(R + "dt_bias", r["heads"], std=0.5)
+            put(R + "norm", r["vdim"], mean=1.0, std=0.1)
+            put(R + "o", D, hv, std=hv ** -0.5)
+    return sd
