@@ -548,11 +548,14 @@ B2TTS_API int b2tts_attn_prep(const void* u, int64_t ldu, int q_off, int k_off, 
 /* Softmax attention with exp(sink[h]) added to the denominator (sink null: none) over the paged cache, this step's keys
  * included.  Token i sees key j <= i with j >= max(0, i - mask + 1) (mask_kind 0, a sliding window) or j >= floor(i / mask) *
  * mask (mask_kind 1, chunks counted from position 0); mask <= 0: every j <= i.  gate (optional): element (t, h) at
- * gate[t * ldg + h]; the head's output is multiplied by its sigmoid.  q [n, heads*dim], out [n, heads*vdim]. */
+ * gate[t * ldg + h]; the head's output is multiplied by its sigmoid.  q [n, heads*dim], out [n, heads*vdim].  max_new >= every
+ * seq_len[b].  path 0 = choose (bf16 prompt portions with head sizes the tensor-core kernel is built for run there, everything
+ * else in the plain kernel), 1 = the plain kernel, 2 = the tensor-core kernel for prompt portions (fails if the sizes do not fit). */
 B2TTS_API int b2tts_sink_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* tok_seq,
-                              const int32_t* positions, const int32_t* seq_len, const int32_t* block_tables, int64_t bt_stride,
-                              const float* sink, const void* gate, int64_t ldg, int n_tokens, int heads, int kv_heads, int dim,
-                              int vdim, int page, int mask_kind, int mask, float scale, int dtype, void* stream);
+                              const int32_t* positions, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
+                              const int32_t* block_tables, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg,
+                              int n_tokens, int n_seqs, int max_new, int heads, int kv_heads, int dim, int vdim, int page,
+                              int mask_kind, int mask, float scale, int dtype, int path, void* stream);
 /* out[t, c] = act(bias[c] + sum_j w[c, j] * u(position(t) - taps + 1 + j)[c_off + c]) for c < channels (act 0: none, 1: SiLU;
  * bias may be null).  Earlier positions come from this step's rows, from state [slots, taps-1, channels] (the sequence's last
  * rows, oldest first, advanced by this call) or are zero before position 0. */

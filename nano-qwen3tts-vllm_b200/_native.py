@@ -102,7 +102,7 @@ def _load():
         "b2tts_stream_mix_norm": (I, [P, P, P, F, F, P, P, P, P, P, I, I, I, F, I, P]),
         "b2tts_stream_gather_norm": (I, [P, P, P, P, P, I, I, I, F, I, P]),
         "b2tts_attn_prep": (I, [P, L, I, I, I, P, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, P]),
-        "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, F, I, P]),
+        "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, I, I, F, I, I, P]),
         "b2tts_short_conv_act": (I, [P, L, I, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, P]),
         "b2tts_gated_group_norm": (I, [P, P, L, P, I, I, I, I, F, P, I, I, I, P]),
         "b2tts_ssm_scan": (I, [P, L, P, L, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
@@ -955,15 +955,19 @@ def attn_prep(u, q_off, k_off, v_off, q_bias, k_bias, v_bias, q_norm_w, k_norm_w
 MASK_WINDOW, MASK_CHUNK = 0, 1
 
 
-def sink_attn(q, k_cache, v_cache, out, lay, sink, gate, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale):
+SINK_ATTN_AUTO, SINK_ATTN_PLAIN, SINK_ATTN_TENSOR = 0, 1, 2
+
+
+def sink_attn(q, k_cache, v_cache, out, lay, sink, gate, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, path=SINK_ATTN_AUTO):
     """``gate``: a column slice [n, heads] of the merged projection (or None)."""
     dt = _act(q, "q")
     assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype and out.is_contiguous()
     assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1)
     _check(_load().b2tts_sink_attn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), lay.tok_seq.data_ptr(),
-                                   lay.positions.data_ptr(), lay.seq_len.data_ptr(), lay.block_tables.data_ptr(),
-                                   lay.block_tables.stride(0), _ptr(sink), _ptr(gate), 0 if gate is None else gate.stride(0),
-                                   lay.n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, dt, _stream()), "sink_attn")
+                                   lay.positions.data_ptr(), lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(),
+                                   lay.block_tables.data_ptr(), lay.block_tables.stride(0), _ptr(sink), _ptr(gate),
+                                   0 if gate is None else gate.stride(0), lay.n_tokens, lay.n_seqs, lay.max_new, heads, kv_heads, dim,
+                                   vdim, page, mask_kind, mask, scale, dt, path, _stream()), "sink_attn")
 
 
 def short_conv_act(u, c_off, channels, w, bias, state, lay, out, taps, act=1):

@@ -52,7 +52,7 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_len,
                  const int32_t* __restrict__ block_tables, int64_t bt_stride, const float* __restrict__ sink,
                  const T* __restrict__ gate, int64_t ldg, int H, int G, int d, int dv, int page, int mask_kind, int mask,
-                 float scale) {
+                 float scale, int only_single) {
   extern __shared__ float smem[];
   float* qs = smem;                                   // [d]
   float* part = smem + ((d + 3) & ~3);                // [SA_WARPS][dv + 2]: sums, running maximum, denominator
@@ -61,6 +61,7 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int b = tok_seq[t];
   T* orow = out + (t * H + h) * dv;
+  if (only_single && seq_len[b] > 1) return;          // the tensor-core kernel owns prompt portions
   if (seq_len[b] <= 0) {                              // padding row
     for (int c = threadIdx.x; c < dv; c += blockDim.x) orow[c] = from_f<T>(0.f);
     return;
@@ -137,6 +138,236 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
   }
 }
 
+
+// ------------------------------------------------------------------ prompt portions on the tensor cores (bf16)
+// 64 query tokens of one head per CTA (4 warps x 16 rows); key tiles of 64 are gathered through the block table into
+// padded shared-memory rows by 16-byte asynchronous copies, two stages deep.  S = Q K^T and O += P V run as m16n8k16 bf16
+// MMAs with float accumulators in registers.  The softmax is the running one: a row keeps its maximum m and denominator
+// l (both in the base-2 domain), rescales O when m grows, and the sink enters as the initial state m = sink, l = 1 with
+// no value.  Weights are computed in float from the float scores and enter the second product as a bf16 pair hi + lo
+// (lo = bf16(w - hi)), i.e. with 16 mantissa bits.  Both masks are a per-row lower bound lo(i) <= j <= i; tiles a warp
+// cannot see are skipped, tiles it sees whole take a path without per-element tests.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
+  hi = pack_bf16(x, y);
+  lo = pack_bf16(x - bf16lo(hi), y - bf16hi(hi));
+}
+
+constexpr int SM_BM = 64, SM_BN = 64;
+
+__device__ __forceinline__ int mask_lo(int i, int mask_kind, int mask) {
+  if (mask <= 0) return 0;
+  return mask_kind == 0 ? max(0, i - mask + 1) : (i / mask) * mask;
+}
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128)
+sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                     const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                     const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
+                     const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int64_t bt_stride,
+                     const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int64_t ldg, int H, int G, int page,
+                     int mask_kind, int mask, float scale) {
+  constexpr int QS = D + 8, VS = DV + 8;             // padded rows: 16-byte aligned, ldmatrix rows land in distinct banks
+  constexpr float LOG2E = 1.4426950408889634f;
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(sm_raw);        // [BM][QS]
+  __nv_bfloat16* Ks = Qs + SM_BM * QS;                                 // [2][BN][QS]
+  __nv_bfloat16* Vs = Ks + 2 * SM_BN * QS;                             // [2][BN][VS]
+  const int b = blockIdx.z, h = blockIdx.y, g = h / (H / G);
+  const int len = seq_len[b];
+  const int t0 = blockIdx.x * SM_BM;
+  if (len <= 1 || t0 >= len) return;                 // one-token and padding rows belong to the plain kernel
+  const int tid = threadIdx.x, lane = tid & 31, wr = tid >> 5;
+  const int start = seq_start[b], pos0 = seq_pos0[b];
+  const int32_t* bt = block_tables + static_cast<int64_t>(b) * bt_stride;
+  for (int idx = tid; idx < SM_BM * (D / 8); idx += 128) {
+    const int r = idx / (D / 8), ch = idx % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t0 + r < len) v = ldg_v4(q + (static_cast<size_t>(start + t0 + r) * H + h) * D + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + r * QS + ch * 8) = v;
+  }
+  const float scale2 = scale * LOG2E;
+  const int t_hi = min(len - 1, t0 + SM_BM - 1);
+  const int j_lo = mask_lo(pos0 + t0, mask_kind, mask), j_hi = pos0 + t_hi;
+  const int row_lo = wr * 16 + (lane >> 2);
+  const int p_lo = pos0 + t0 + row_lo, p_hi = p_lo + 8;
+  const bool ok_lo = t0 + row_lo < len, ok_hi = t0 + row_lo + 8 < len;
+  const int lo_lo = mask_lo(p_lo, mask_kind, mask), lo_hi = mask_lo(p_hi, mask_kind, mask);
+  const int wp_lo = pos0 + t0 + wr * 16, wp_hi = wp_lo + 15;
+  const int w_first = mask_lo(wp_lo, mask_kind, mask), w_last = mask_lo(wp_hi, mask_kind, mask);
+  float oacc[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
+  // running maximum and (this thread's share of the) denominator of its two rows; the sink is counted by one lane of four
+  float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
+  if (sink != nullptr) {
+    m0 = m1 = sink[h] * LOG2E;
+    if ((lane & 3) == 0) l0 = l1 = 1.f;
+  }
+
+  // two threads per key: the slot once, then the thread's 16-byte chunks lch, lch + 2, ... of the key's K and V rows
+  const int lkey = tid >> 1, lch = tid & 1;
+  auto load_tile = [&](int stage, int j0) {
+    const int j = j0 + lkey;
+    const bool ok = j <= j_hi;
+    size_t slot = 0;
+    if (ok) {
+      const int pg = j / page;
+      slot = static_cast<size_t>(bt[pg]) * page + (j - pg * page);
+    }
+    const __nv_bfloat16* ksrc = k_cache + (slot * G + g) * D + lch * 8;
+    const __nv_bfloat16* vsrc = v_cache + (slot * G + g) * DV + lch * 8;
+    __nv_bfloat16* kd = Ks + (stage * SM_BN + lkey) * QS + lch * 8;
+    __nv_bfloat16* vd = Vs + (stage * SM_BN + lkey) * VS + lch * 8;
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) cp_async_16(kd + i * 16, ksrc + i * 16, ok);
+#pragma unroll
+    for (int i = 0; i < DV / 16; ++i) cp_async_16(vd + i * 16, vsrc + i * 16, ok);
+  };
+  const int n_tiles = (j_hi - j_lo) / SM_BN + 1;
+  load_tile(0, j_lo);
+  cp_async_commit();
+  for (int t = 0; t < n_tiles; ++t) {
+    const int j0 = j_lo + t * SM_BN;
+    cp_async_wait<0>();
+    __syncthreads();                                 // tile t has landed (Q too); tile t - 1 is consumed
+    if (t + 1 < n_tiles) load_tile((t + 1) & 1, j0 + SM_BN);
+    cp_async_commit();
+    const __nv_bfloat16* Kt = Ks + (t & 1) * SM_BN * QS;
+    const __nv_bfloat16* Vt = Vs + (t & 1) * SM_BN * VS;
+    if (j0 > wp_hi || j0 + SM_BN - 1 < w_first || t0 + wr * 16 >= len) continue;     // none of the warp's rows sees the tile
+    float sacc[SM_BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < SM_BN / 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sacc[i][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a[4];
+      ldsm_x4(a[0], a[1], a[2], a[3], Qs + (wr * 16 + (lane & 15)) * QS + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < SM_BN / 16; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(b0, b1, b2, b3, Kt + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * QS + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16_16816(sacc[2 * np], a, b0, b1);
+        mma_bf16_16816(sacc[2 * np + 1], a, b2, b3);
+      }
+    }
+    const bool inner = j0 + SM_BN - 1 <= wp_lo && j0 >= w_last;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < SM_BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float s = sacc[nt][e] * scale2;
+        if (!inner) {
+          const int j = j0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+          const bool ok = e < 2 ? (j <= p_lo && j >= lo_lo) : (j <= p_hi && j >= lo_hi);
+          if (!ok) s = -INFINITY;
+        }
+        sacc[nt][e] = s;
+        if (e < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);      // finite: m starts finite
+    const float c0 = ex2_approx(m0 - n0), c1 = ex2_approx(m1 - n1);
+    m0 = n0; m1 = n1;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < SM_BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float w = ex2_approx(sacc[nt][e] - (e < 2 ? n0 : n1));
+        sacc[nt][e] = w;
+        if (e < 2) s0 += w; else s1 += w;
+      }
+    }
+    l0 = l0 * c0 + s0;
+    l1 = l1 * c1 + s1;
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) { oacc[i][0] *= c0; oacc[i][1] *= c0; oacc[i][2] *= c1; oacc[i][3] *= c1; }
+#pragma unroll
+    for (int kk = 0; kk < SM_BN / 16; ++kk) {
+      uint32_t ah[4], al[4];
+      split_bf16(sacc[2 * kk][0], sacc[2 * kk][1], ah[0], al[0]);
+      split_bf16(sacc[2 * kk][2], sacc[2 * kk][3], ah[1], al[1]);
+      split_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1], ah[2], al[2]);
+      split_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3], ah[3], al[3]);
+#pragma unroll
+      for (int np = 0; np < DV / 16; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(b0, b1, b2, b3, Vt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VS + np * 16 + (lane >> 4) * 8);
+        mma_bf16_16816(oacc[2 * np], ah, b0, b1);
+        mma_bf16_16816(oacc[2 * np], al, b0, b1);
+        mma_bf16_16816(oacc[2 * np + 1], ah, b2, b3);
+        mma_bf16_16816(oacc[2 * np + 1], al, b2, b3);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    if (!(half ? ok_hi : ok_lo)) continue;
+    const size_t row = static_cast<size_t>(start + t0 + row_lo + 8 * half);
+    float inv = 1.0f / (half ? l1 : l0);
+    if (gate != nullptr) inv *= sigmoid_f(__bfloat162float(gate[row * ldg + h]));
+    __nv_bfloat16* o = out + (row * H + h) * DV + 2 * (lane & 3);
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt)
+      *reinterpret_cast<uint32_t*>(o + nt * 8) = pack_bf16(oacc[nt][2 * half] * inv, oacc[nt][2 * half + 1] * inv);
+  }
+}
+
+template <int D, int DV>
+static cudaError_t launch_sink_mma(int max_new, int n_seqs, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
+                                   const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
+                                   int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int H, int G, int page,
+                                   int mask_kind, int mask, float scale) {
+  auto kern = sink_attn_mma_kernel<D, DV>;
+  const size_t smem = sizeof(__nv_bfloat16) * ((SM_BM + 2 * SM_BN) * (D + 8) + 2 * SM_BN * (DV + 8));
+  static bool opted = false;
+  if (!opted) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    opted = true;
+  }
+  using B = __nv_bfloat16;
+  const dim3 grid((max_new + SM_BM - 1) / SM_BM, H, n_seqs);
+  kern<<<grid, 128, smem, st>>>(static_cast<const B*>(q), static_cast<const B*>(kc), static_cast<const B*>(vc), static_cast<B*>(out),
+                                seq_start, seq_pos0, seq_len, bt, bt_stride, sink, static_cast<const B*>(gate), ldg, H, G, page,
+                                mask_kind, mask, scale);
+  return cudaSuccess;
+}
+
+// head sizes the tensor-core kernel is built for
+static bool sink_mma_shape(int d, int dv) {
+  return (d == 32 || d == 48 || d == 64 || d == 96 || d == 128) && (dv == 64 || dv == 128);
+}
+
+#define SINK_MMA_ARGS max_new, n_seqs, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, H, G, page, mask_kind, mask, scale
+template <int D>
+static cudaError_t launch_sink_mma_dv(int dv, int max_new, int n_seqs, cudaStream_t st, const void* q, const void* kc, const void* vc,
+                                      void* out, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
+                                      const int32_t* bt, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int H,
+                                      int G, int page, int mask_kind, int mask, float scale) {
+  return dv == 64 ? launch_sink_mma<D, 64>(SINK_MMA_ARGS) : launch_sink_mma<D, 128>(SINK_MMA_ARGS);
+}
+
 }  // namespace row
 }  // namespace b2
 
@@ -144,30 +375,50 @@ using namespace b2;
 using namespace b2::row;
 
 extern "C" int b2tts_sink_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* tok_seq,
-                               const int32_t* positions, const int32_t* seq_len, const int32_t* block_tables, int64_t bt_stride,
-                               const float* sink, const void* gate, int64_t ldg, int n_tokens, int heads, int kv_heads, int dim,
-                               int vdim, int page, int mask_kind, int mask, float scale, int dtype, void* stream) {
-  B2_REQUIRE(n_tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && page > 0, B2TTS_EINVAL,
-             "sink_attn: bad sizes (heads=%d kv_heads=%d dim=%d vdim=%d page=%d)", heads, kv_heads, dim, vdim, page);
+                               const int32_t* positions, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
+                               const int32_t* block_tables, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg,
+                               int n_tokens, int n_seqs, int max_new, int heads, int kv_heads, int dim, int vdim, int page,
+                               int mask_kind, int mask, float scale, int dtype, int path, void* stream) {
+  B2_REQUIRE(n_tokens >= 0 && n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && page > 0,
+             B2TTS_EINVAL, "sink_attn: bad sizes (heads=%d kv_heads=%d dim=%d vdim=%d page=%d)", heads, kv_heads, dim, vdim, page);
   B2_REQUIRE(vdim <= 32 * SA_MAX_PER_LANE, B2TTS_EUNSUPPORTED, "sink_attn: value size %d above %d", vdim, 32 * SA_MAX_PER_LANE);
-  B2_REQUIRE(heads <= 65535, B2TTS_EUNSUPPORTED, "sink_attn: %d heads", heads);
+  B2_REQUIRE(heads <= 65535 && n_seqs <= 65535, B2TTS_EUNSUPPORTED, "sink_attn: %d heads, %d sequences", heads, n_seqs);
   B2_REQUIRE(mask_kind == 0 || mask_kind == 1, B2TTS_EINVAL, "sink_attn: mask kind %d", mask_kind);
+  B2_REQUIRE(path >= 0 && path <= 2, B2TTS_EINVAL, "sink_attn: path %d", path);
   B2_REQUIRE(B2_ROW_DTYPE_OK(dtype), B2TTS_EINVAL, "sink_attn: dtype %d", dtype);
-  if (n_tokens == 0) return B2TTS_OK;
-  B2_REQUIRE(q && k_cache && v_cache && out && tok_seq && positions && seq_len && block_tables, B2TTS_EINVAL, "sink_attn: null pointer");
+  if (n_tokens == 0 || n_seqs == 0) return B2TTS_OK;
+  B2_REQUIRE(q && k_cache && v_cache && out && tok_seq && positions && seq_start && seq_pos0 && seq_len && block_tables, B2TTS_EINVAL,
+             "sink_attn: null pointer");
   B2_REQUIRE(aligned16(k_cache) && aligned16(v_cache), B2TTS_EALIGN, "sink_attn: caches must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool mma_ok = dtype == B2TTS_DTYPE_BF16 && sink_mma_shape(dim, vdim) && aligned16(q) && aligned16(out);
+  B2_REQUIRE(path != 2 || mma_ok, B2TTS_EUNSUPPORTED, "sink_attn: the tensor-core kernel takes bf16 with head sizes 32..128 / 64, 128");
+  const bool use_mma = mma_ok && path != 1 && max_new > 1;
+  if (use_mma) {
+    const int H = heads, G = kv_heads;
+    const void* kc = k_cache; const void* vc = v_cache; const int32_t* bt = block_tables;
+    cudaError_t e;
+    switch (dim) {
+      case 32: e = launch_sink_mma_dv<32>(vdim, SINK_MMA_ARGS); break;
+      case 48: e = launch_sink_mma_dv<48>(vdim, SINK_MMA_ARGS); break;
+      case 64: e = launch_sink_mma_dv<64>(vdim, SINK_MMA_ARGS); break;
+      case 96: e = launch_sink_mma_dv<96>(vdim, SINK_MMA_ARGS); break;
+      default: e = launch_sink_mma_dv<128>(vdim, SINK_MMA_ARGS); break;
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "sink_attn (tensor cores)");
+    B2_CHECK_LAUNCH("sink_attn (tensor cores)");
+  }
   const size_t sm = (((dim + 3) & ~3) + SA_WARPS * (vdim + 2)) * sizeof(float);
   const dim3 grid(n_tokens, heads);
   if (dtype == B2TTS_DTYPE_BF16)
     sink_attn_kernel<__nv_bfloat16><<<grid, SA_WARPS * 32, sm, st>>>(static_cast<const __nv_bfloat16*>(q),
         static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache), static_cast<__nv_bfloat16*>(out), tok_seq,
         positions, seq_len, block_tables, bt_stride, sink, static_cast<const __nv_bfloat16*>(gate), ldg, heads, kv_heads, dim, vdim, page,
-        mask_kind, mask, scale);
+        mask_kind, mask, scale, use_mma ? 1 : 0);
   else
     sink_attn_kernel<float><<<grid, SA_WARPS * 32, sm, st>>>(static_cast<const float*>(q), static_cast<const float*>(k_cache),
         static_cast<const float*>(v_cache), static_cast<float*>(out), tok_seq, positions, seq_len, block_tables, bt_stride, sink,
-        static_cast<const float*>(gate), ldg, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale);
+        static_cast<const float*>(gate), ldg, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, 0);
   B2_CHECK_LAUNCH("sink_attn");
   return B2TTS_OK;
 }

@@ -136,7 +136,7 @@ def test_attention_preparation_bias_whole_norm_rotation_and_cache_rows(nat, H, G
     assert not kc.view(-1, nk).cpu()[untouched].any() and not vc.view(-1, nv).cpu()[untouched].any()
 
 
-def _attn_case(nat, H, G, d, dv, kind, mask, page, seqs, dtype=torch.float32, spike=None, sink_big=None, gate=False, seed=0):
+def _attn_case(nat, H, G, d, dv, kind, mask, page, seqs, dtype=torch.float32, spike=None, sink_big=None, gate=False, seed=0, path=0):
     """``seqs`` = [(cached, new)]: sequences whose first ``cached`` tokens are in the cache and whose last ``new`` run now.
     ``spike`` = (sequence, query position, key position): that key is made to take that query's softmax in head 0."""
     g = torch.Generator().manual_seed(seed)
@@ -175,7 +175,7 @@ def _attn_case(nat, H, G, d, dv, kind, mask, page, seqs, dtype=torch.float32, sp
     gd = torch.cat(gates).to(DEV) if gate else None
     out = torch.empty(lay.n_tokens, H * dv, dtype=dtype, device=DEV)
     nat.sink_attn(qd, kc.to(dtype).to(DEV), vc.to(dtype).to(DEV), out, lay, sink.to(DEV), gd, H, G, d, dv, page,
-                  nat.MASK_WINDOW if kind == "window" else nat.MASK_CHUNK, mask, scale)
+                  nat.MASK_WINDOW if kind == "window" else nat.MASK_CHUNK, mask, scale, path)
     return out, torch.cat(refs)
 
 
@@ -188,17 +188,31 @@ def test_sink_attention_prompts_portions_and_decoded_tokens_in_one_launch(nat, H
     assert rel(out, ref) < 2e-5
 
 
+@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 64, 64), (2, 1, 48, 64), (4, 4, 128, 128), (3, 1, 32, 128), (2, 2, 96, 64), (2, 1, 128, 64)])
+@pytest.mark.parametrize("kind,mask", [("window", 1), ("window", 7), ("window", 64), ("window", 65), ("window", 130), ("chunk", 1),
+                                       ("chunk", 5), ("chunk", 64), ("chunk", 100)])
+def test_tensor_core_sink_attention_against_plain_model_and_plain_kernel(nat, H, G, d, dv, kind, mask):
+    """bfloat16 prompt portions on the tensor cores (decoded tokens of the same launch in the plain kernel): the error
+    against the float64 model is that of the plain bfloat16 kernel."""
+    seqs = [(0, 70), (130, 1), (33, 140), (64, 2), (0, 1), (199, 3), (5, 64)]
+    tc, ref = _attn_case(nat, H, G, d, dv, kind, mask, 16, seqs, torch.bfloat16, gate=(H % 2 == 0), seed=mask, path=nat.SINK_ATTN_TENSOR)
+    plain, _ = _attn_case(nat, H, G, d, dv, kind, mask, 16, seqs, torch.bfloat16, gate=(H % 2 == 0), seed=mask, path=nat.SINK_ATTN_PLAIN)
+    assert rel(plain, ref) < 1.5e-2 and rel(tc, ref) < 1.5e-2
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("page", [16, 64])
 @pytest.mark.parametrize("kind,mask", [("window", 33), ("window", 64), ("window", 200), ("chunk", 33), ("chunk", 64), ("chunk", 200)])
 def test_one_key_that_takes_the_softmax_at_mask_edges_and_page_borders(nat, dtype, tol, page, kind, mask):
     """The query at position i, in a prompt portion and as a decoded token; the dominant key at the first position the
-    mask lets through and at the one before it (which must NOT be seen), and at the query itself."""
+    mask lets through and at the one before it (which must NOT be seen), and at the query itself.  In bfloat16 the
+    head size is one the tensor-core kernel takes, so prompt portions run there and decoded tokens in the plain kernel."""
+    hd = 64 if dtype == torch.bfloat16 else 16
     for i in (mask - 1, mask, 2 * mask - 1, 2 * mask, 256):
         lo = max(0, i - mask + 1) if kind == "window" else (i // mask) * mask
         for kj in {lo, max(lo - 1, 0), i, (i // page) * page, max((i // page) * page - 1, 0)}:
             for cached, new in ((i, 1), (max(i - 9, 0), 14)):
-                out, ref = _attn_case(nat, 4, 2, 16, 16, kind, mask, page, [(3, 2), (cached, new)], dtype, spike=(1, i, kj), seed=i + kj)
+                out, ref = _attn_case(nat, 4, 2, hd, hd, kind, mask, page, [(3, 2), (cached, new)], dtype, spike=(1, i, kj), seed=i + kj)
                 assert rel(out, ref) < tol, (i, kj, cached, new)
 
 
@@ -206,6 +220,11 @@ def test_one_key_that_takes_the_softmax_at_mask_edges_and_page_borders(nat, dtyp
 def test_far_key_among_hundreds_and_a_sink_that_swallows_a_head(nat, dtype, tol):
     out, ref = _attn_case(nat, 4, 1, 32, 24, "window", 700, 64, [(0, 650), (649, 1)], dtype, spike=(0, 640, 3), seed=1)
     assert rel(out, ref) < tol
+    if dtype == torch.bfloat16:                                           # the same through the tensor-core kernel
+        out, ref = _attn_case(nat, 4, 1, 32, 64, "window", 700, 64, [(0, 650), (649, 1)], dtype, spike=(0, 640, 3), seed=1)
+        assert rel(out, ref) < tol
+        out, ref = _attn_case(nat, 4, 2, 64, 64, "window", 50, 16, [(0, 80), (79, 1)], dtype, sink_big=2, seed=3)
+        assert rel(out, ref) < tol and out.view(-1, 4, 64)[:, 2].abs().max().item() < 1e-9
     out, ref = _attn_case(nat, 4, 1, 32, 24, "chunk", 1000, 64, [(645, 1)], dtype, spike=(0, 645, 2), seed=2)
     assert rel(out, ref) < tol
     out, ref = _attn_case(nat, 4, 2, 16, 16, "window", 50, 16, [(0, 80), (79, 1)], dtype, sink_big=2, seed=3)
