@@ -60,6 +60,9 @@ def parse():
     ap.add_argument("--lm-latent", action="store_true",
                     help="instead of the frame loop: the Ridevik decoder (latent attention) beside Bokenex at equal layer sizes, "
                          "plus the kernels of both against their rooflines (bench_lm.py); one JSON line")
+    ap.add_argument("--lm-hybrid", action="store_true",
+                    help="instead of the frame loop: the Tibivik decoder (residual streams, attention beside recurrences) beside "
+                         "Bokenex at equal layer sizes, plus the kernels of both against their rooflines (bench_lm.py); one JSON line")
     return ap.parse_args()
 
 
@@ -483,10 +486,11 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(device))
     barrier = (lambda: (dist.barrier(), torch.cuda.synchronize())) if dist else None
 
-    if a.lm or a.lm_latent:
+    if a.lm or a.lm_latent or a.lm_hybrid:
         import bench_lm
         if rank == 0:
-            print(json.dumps(bench_lm.main_latent(device) if a.lm_latent else bench_lm.main(device)), flush=True)
+            run = bench_lm.main_hybrid if a.lm_hybrid else bench_lm.main_latent if a.lm_latent else bench_lm.main
+            print(json.dumps(run(device)), flush=True)
         return
 
     total_frames = a.steps + a.warmup + 8

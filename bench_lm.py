@@ -68,7 +68,7 @@ def bench_bokenex(s: dict, moe: bool, device: str, design: str = "bokenex") -> d
     import torch
     from nano_qwen3tts_vllm_b200.engine.llm_engine.lm_engine import CausalLMEngine
     from nano_qwen3tts_vllm_b200.sampling_params import SamplingParams
-    cfg = bokenex_config(s, moe) if design == "bokenex" else ridevik_config(s, moe)
+    cfg = {"bokenex": bokenex_config, "ridevik": ridevik_config, "tibivik": tibivik_config}[design](s, moe)
     pages = DECODE_SEQS * ((DECODE_CTX + 64 + PAGE - 1) // PAGE) + PREFILL_SEQS * (PREFILL_LEN // PAGE + 1)
     eng = CausalLMEngine(cfg, state_dict="random:7", kvcache_block_size=PAGE, num_kvcache_blocks=pages,
                          max_num_seqs=DECODE_SEQS + PREFILL_SEQS, max_model_len=4096, max_num_batched_tokens=16384,
@@ -410,6 +410,188 @@ def bench_latent_kernels(device: str) -> dict:
     ms = timed(lambda: nat.gate_heads(v, (dv, n * dv), u[:, qrank + Dk:], ho, H, dv))
     res["gate_heads 8192 tokens"] = entry(ms, bytes_=n * H * dv * 2 * 3)
     return res
+
+
+def tibivik_config(s: dict, moe: bool = False):
+    """Layers of real hybrid models' shapes at the size's width: a state-space layer (2 x width inner channels in heads of
+    64, 128 state numbers, 4 taps), a chunked attention of the size's head layout beside a delta rule (as many value
+    heads of the same size, half as many key heads), and a windowed attention with values tied to the keys beside a matrix
+    memory of half as many heads; two residual streams, a hashed bigram table, SiLU-gated feed-forwards with the
+    talker's three matrices."""
+    from nano_qwen3tts_vllm_b200.config import TibivikConfig
+    d, H, G, W = s["dim"], s["heads"], s["kv_heads"], s["width"]
+    mlp = {"kind": "dense", "ff": s["inter"]}
+    ssm = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 1, "conv": TAPS, "norm_groups": 1}}
+    chunk = {"type": "parallel_2", "mlp": mlp,
+             "mixer": {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "mask": {"size": WINDOW}, "scale": d ** -0.5},
+                       "right": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "conv": TAPS}, "left_scale": 0.5, "right_scale": 1.0}}
+    window = {"type": "parallel", "mlp": mlp,
+              "mixer": {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "mask": {"size": WINDOW}, "scale": d ** -0.5,
+                                 "rot": {"dims": d // 2, "base": 1e4}},
+                        "right": {"heads": H // 2, "dim": d, "vdim": d, "gate_cap": 10.0}, "left_scale": 0.5, "right_scale": 1.0}}
+    return TibivikConfig.from_dict({"architecture": "Tibivik", "vocab": 3072, "width": W, "norm": {"eps": 1e-6}, "streams": 2,
+                                    "embedding": {"bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 17}},
+                                    "layers": [ssm, chunk, window, chunk][:LAYERS]})
+
+
+def bench_hybrid_kernels(device: str) -> dict:
+    """Tibivik's own kernels at the w2048 layer shapes, each after an L2 flush, with the fraction of the measured roofline;
+    the like kernels of Bokenex come from ``bench_kernels`` in the same run."""
+    import torch
+    import nano_qwen3tts_vllm_b200._native as nat
+    hbm, tflops, how = _peaks()
+    dev = torch.device(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    BF = torch.bfloat16
+
+    def timed(fn, iters=5):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    class Lay:
+        pass
+
+    def layout(n_seqs, cached, new, pages_per_seq):
+        lay = Lay()
+        i32 = dict(dtype=torch.int32, device=dev)
+        lay.n_seqs, lay.max_new, lay.n_tokens = n_seqs, new, n_seqs * new
+        lay.seq_start = torch.arange(n_seqs, **i32) * new
+        lay.seq_pos0 = torch.full((n_seqs,), cached, **i32)
+        lay.seq_len = torch.full((n_seqs,), new, **i32)
+        lay.seq_slot = torch.arange(n_seqs, **i32)
+        lay.block_tables = torch.arange(n_seqs * pages_per_seq, **i32).view(n_seqs, pages_per_seq).contiguous()
+        pos = (torch.arange(new, **i32) + cached).repeat(n_seqs)
+        lay.positions = pos
+        lay.tok_seq = torch.arange(n_seqs, **i32).repeat_interleave(new)
+        lay.slot_mapping = (lay.tok_seq * pages_per_seq * PAGE + pos).to(torch.int32)
+        return lay
+
+    def entry(ms, bytes_=None, flops=None):
+        e = {"us": round(ms * 1e3, 1)}
+        if bytes_ is not None:
+            e["gbs"] = round(bytes_ / ms / 1e6, 1)
+            e["frac_hbm"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 1)
+            e["frac_tensor"] = round(flops / ms / 1e9 / tflops, 4)
+        return e
+
+    H, G, d, D = 16, 8, 128, 2048
+    res = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how}}
+    sink = torch.zeros(H, device=dev)
+    scale = d ** -0.5
+
+    def attn(lay, kc, vc, kind):
+        n = lay.n_tokens
+        q = torch.randn(n, H * d, device=dev).to(BF)
+        out = torch.empty(n, H * d, dtype=BF, device=dev)
+        return lambda: nat.sink_attn(q, kc, vc, out, lay, sink, None, H, G, d, d, PAGE, kind, WINDOW, scale)
+
+    pps = (DECODE_CTX + PAGE) // PAGE + 1
+    kc = torch.randn(DECODE_SEQS * pps, PAGE, G * d, device=dev).to(BF)
+    vc = torch.randn(DECODE_SEQS * pps, PAGE, G * d, device=dev).to(BF)
+    lay = layout(DECODE_SEQS, DECODE_CTX, 1, pps)
+    res["sink_attn decode 64x1100 window 1024"] = entry(timed(attn(lay, kc, vc, nat.MASK_WINDOW)), bytes_=DECODE_SEQS * WINDOW * G * d * 2 * 2)
+    res["sink_attn decode 64x1100 chunk 1024"] = entry(timed(attn(lay, kc, vc, nat.MASK_CHUNK)),
+                                                        bytes_=DECODE_SEQS * (DECODE_CTX % WINDOW + 1) * G * d * 2 * 2)
+    lay = layout(PREFILL_SEQS, 0, PREFILL_LEN, PREFILL_LEN // PAGE)
+    n = PREFILL_SEQS * PREFILL_LEN
+    pairs_w = PREFILL_SEQS * sum(min(i + 1, WINDOW) for i in range(PREFILL_LEN))
+    res["sink_attn prefill 4x2048 window 1024"] = entry(timed(attn(lay, kc, vc, nat.MASK_WINDOW), iters=3), flops=pairs_w * H * 2 * d * 2)
+    pairs_c = PREFILL_SEQS * sum(i % WINDOW + 1 for i in range(PREFILL_LEN))
+    res["sink_attn prefill 4x2048 chunk 1024"] = entry(timed(attn(lay, kc, vc, nat.MASK_CHUNK), iters=3), flops=pairs_c * H * 2 * d * 2)
+    # ---- attention preparation: whole-projection norm, rotation, cache write (values = raw keys)
+    from nano_qwen3tts_vllm_b200.layers.rotary_embedding import HalfRotary
+    rot = HalfRotary(d // 2, 1e4).to(dev)
+    u = torch.randn(n, H * d + G * d, device=dev).to(BF)
+    qo = torch.empty(n, H * d, dtype=BF, device=dev)
+    wq, wk = torch.ones(H * d, device=dev), torch.ones(G * d, device=dev)
+    ms = timed(lambda: nat.attn_prep(u, 0, H * d, -1, None, None, None, wq, wk, rot.freq, d // 2, lay, qo, kc, vc, H, G, d, d, 1e-6))
+    res["attn_prep 8192 tokens"] = entry(ms, bytes_=n * (H * d * 2 + G * d * 3) * 2)
+    # ---- residual streams: update + read-out + norm
+    xs = torch.randn(n, 2, D, device=dev)
+    y1, y2 = torch.randn(n, D, device=dev).to(BF), torch.randn(n, D, device=dev).to(BF)
+    mix, ow, iw, w = torch.eye(2, device=dev), torch.ones(2, device=dev), torch.ones(2, device=dev), torch.ones(D, device=dev)
+    h = torch.empty(n, D, dtype=BF, device=dev)
+    ms = timed(lambda: nat.stream_mix_norm(xs, y1, y2, 0.7, 1.3, mix, ow, iw, w, h, 1e-6, BF))
+    res["stream_mix_norm 8192x2x2048"] = entry(ms, bytes_=n * D * (2 * 4 * 2 + 2 * 2 + 2))
+    # ---- short convolution + SiLU over the state-space layer's channels
+    C = 2 * D + 256
+    uc = torch.randn(n, C, device=dev).to(BF)
+    cw = torch.randn(C, TAPS, device=dev)
+    cst = torch.zeros(DECODE_SEQS, TAPS - 1, C, dtype=BF, device=dev)
+    co = torch.empty(n, C, dtype=BF, device=dev)
+    ms = timed(lambda: nat.short_conv_act(uc, 0, C, cw, None, cst, lay, co, TAPS, 1))
+    res["short_conv_act 8192 tokens x 4352 channels"] = entry(ms, bytes_=n * C * 2 * 2)
+    # ---- recurrences: prompt portions (4 x 2048 tokens) and decode steps (64 sequences)
+    dlay = layout(DECODE_SEQS, DECODE_CTX, 1, 1)
+    Hs, dvs, N = 2 * D // 64, 64, 128
+    hz = torch.zeros(Hs, device=dev)
+    for name, ly, nn in (("prefill 4x2048", lay, n), ("decode 64", dlay, DECODE_SEQS)):
+        seqs = ly.n_seqs
+        xbc = torch.randn(nn, Hs * dvs + 2 * N, device=dev).to(BF)
+        dt = torch.randn(nn, Hs, device=dev).to(BF)
+        st = torch.zeros(seqs, Hs, N, dvs, device=dev)
+        yo = torch.empty(nn, Hs * dvs, device=dev)
+        ms = timed(lambda: nat.ssm_scan(xbc, dt, hz, hz, hz, st, yo, ly, Hs, 1, dvs, N), iters=3)
+        res[f"ssm_scan {name} (64 heads x 64, state 128)"] = entry(ms, bytes_=seqs * Hs * N * dvs * 4 * 2 + nn * (Hs * dvs * 6 + 2 * N * 2),
+                                                                  flops=nn * Hs * N * dvs * 4)
+        qkv = torch.randn(nn, 2 * G * d + H * d, device=dev).to(BF)
+        ba = torch.randn(nn, 2 * H, device=dev).to(BF)
+        st2 = torch.zeros(seqs, H, d, d, device=dev)
+        o2 = torch.empty(nn, H * d, device=dev)
+        hz2 = torch.zeros(H, device=dev)
+        ms = timed(lambda: nat.delta_rule_scan(qkv, ba[:, :H], ba[:, H:], hz2, hz2, st2, o2, ly, H, G, d, d), iters=3)
+        res[f"delta_rule_scan {name} (16 heads, 128 x 128)"] = entry(ms, bytes_=seqs * H * d * d * 4 * 2 + nn * (2 * G * d * 2 + H * d * 6),
+                                                                    flops=nn * H * d * d * 8)
+        Hm = H // 2
+        um = torch.randn(nn, 3 * Hm * d + 2 * Hm, device=dev).to(BF)
+        st3 = torch.zeros(seqs, Hm, d, d, device=dev)
+        nm = torch.zeros(seqs, Hm, d + 1, device=dev)
+        gs = torch.empty(nn, Hm, 3, device=dev)
+        o3 = torch.empty(nn, Hm * d, device=dev)
+        hz3 = torch.zeros(Hm, device=dev)
+        cut = lambda a, w_: um[:, a:a + w_]
+        ms = timed(lambda: nat.matrix_memory_scan(cut(0, Hm * d), cut(Hm * d, Hm * d), cut(2 * Hm * d, Hm * d), cut(3 * Hm * d, Hm),
+                                                  cut(3 * Hm * d + Hm, Hm), hz3, hz3, 10.0, st3, nm, gs, o3, ly, Hm, d, d), iters=3)
+        res[f"matrix_memory_scan {name} (8 heads, 128 x 128)"] = entry(ms, bytes_=seqs * Hm * d * d * 4 * 2 + nn * Hm * d * (6 + 4),
+                                                                      flops=nn * Hm * d * d * 4)
+    yy = torch.randn(n, H * d, device=dev)
+    gg = torch.randn(n, H * d, device=dev).to(BF)
+    oo = torch.empty(n, H * d, dtype=BF, device=dev)
+    wn = torch.ones(d, device=dev)
+    ms = timed(lambda: nat.gated_group_norm(yy, gg, wn, H, nat.GATE_SILU, False, 1e-6, oo))
+    res["gated_group_norm 8192x2048 (16 heads)"] = entry(ms, bytes_=n * H * d * (4 + 2 + 2))
+    return res
+
+
+def main_hybrid(device: str = "cuda:0") -> dict:
+    """``bench.py --lm-hybrid``: Tibivik beside Bokenex (the package's closest model: a token-id decoder with a short
+    convolution and windowed attention over the same engine) at equal width, layer count and feed-forward parameters, then
+    the kernels of both against their rooflines."""
+    import torch
+    t0 = time.time()
+    out = {"metric": "lm_prefill_decode_throughput", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights)",
+           "config": {"prefill": f"{PREFILL_SEQS}x{PREFILL_LEN} tokens per step", "decode": f"{DECODE_SEQS} sequences at context {DECODE_CTX}",
+                      "layers": LAYERS, "window": WINDOW, "conv_taps": TAPS, "page": PAGE}, "sizes": {}}
+    for name, s in SIZES.items():
+        row = {"tibivik": bench_bokenex(s, False, device, "tibivik"), "bokenex_dense": bench_bokenex(s, False, device)}
+        out["sizes"][name] = row
+        torch.cuda.empty_cache()
+    out["kernels"] = bench_hybrid_kernels(device)
+    out["like_kernels"] = bench_kernels(device)
+    out["seconds"] = round(time.time() - t0, 1)
+    return out
 
 
 def main_latent(device: str = "cuda:0") -> dict:

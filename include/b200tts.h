@@ -569,18 +569,20 @@ B2TTS_API int b2tts_gated_group_norm(const float* y, const void* gate, int64_t l
                                      int gate_act, int gate_first, float eps, void* out, int rows, int cols, int dtype, void* stream);
 /* State-space recurrence per head h (group g = h / (heads / groups)), state [slots, heads, dim, vdim] float:
  * dt = softplus(dt_in[t, h] + dt_bias[h]); S <- exp(-exp(a_log[h]) dt) S + dt B_t x_t^T; out[t, h] = S^T C_t + d_skip[h] x_t, with
- * row t of xbc = [x: heads*vdim | B: groups*dim | C: groups*dim] (after its convolution and activation).  out [rows, heads*vdim]. */
+ * row t of xbc = [x: heads*vdim | B: groups*dim | C: groups*dim] (after its convolution and activation).  out [rows, heads*vdim];
+ * coef [rows, heads, 3] float is scratch (the per-token scalars, computed by a kernel in front of the recurrence). */
 B2TTS_API int b2tts_ssm_scan(const void* xbc, int64_t ldx, const void* dt, int64_t lddt, const float* dt_bias, const float* a_log,
-                             const float* d_skip, float* state, float* out, const int32_t* seq_start, const int32_t* seq_pos0,
-                             const int32_t* seq_len, const int32_t* seq_slot, int n_seqs, int heads, int groups, int vdim, int dim,
-                             int dtype, void* stream);
+                             const float* d_skip, float* state, float* coef, float* out, const int32_t* seq_start,
+                             const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot, int n_tokens, int n_seqs,
+                             int heads, int groups, int vdim, int dim, int dtype, void* stream);
 /* Delta rule per head, state [slots, heads, dim, vdim] float: row t of qkv = [q: kv_heads*dim | k: kv_heads*dim | v: heads*vdim];
  * q and k are made unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times dim^(-1/2); g = exp(-exp(a_log[h]) softplus(a_in[t, h] +
- * dt_bias[h])), beta = sigmoid(beta_in[t, h]); S <- g S; u = beta (v - S^T k); S <- S + k u^T; out[t, h] = S^T q. */
+ * dt_bias[h])), beta = sigmoid(beta_in[t, h]); S <- g S; u = beta (v - S^T k); S <- S + k u^T; out[t, h] = S^T q.
+ * coef [rows, heads, 3] float is scratch. */
 B2TTS_API int b2tts_delta_rule_scan(const void* qkv, int64_t ldq, const void* beta, const void* a_in, int64_t ldu, const float* a_log,
-                                    const float* dt_bias, float* state, float* out, const int32_t* seq_start, const int32_t* seq_pos0,
-                                    const int32_t* seq_len, const int32_t* seq_slot, int n_seqs, int heads, int kv_heads, int dim,
-                                    int vdim, int dtype, void* stream);
+                                    const float* dt_bias, float* state, float* coef, float* out, const int32_t* seq_start,
+                                    const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot, int n_tokens, int n_seqs,
+                                    int heads, int kv_heads, int dim, int vdim, int dtype, void* stream);
 /* Matrix memory with exponential gates per head: i = cap tanh((ig[t, h] + i_bias[h]) / cap), f = logsigmoid(cap tanh((fg[t, h] +
  * f_bias[h]) / cap)); m' = max(f + m, i) (m starts at 0); S <- exp(f + m - m') S + exp(i - m') k v^T, n likewise with k alone;
  * out[t, h] = S^T q / (max(|n . q|, exp(-m')) + 1e-6) with q times dim^(-1/2).  q, k [rows, heads*dim] and v [rows, heads*vdim]

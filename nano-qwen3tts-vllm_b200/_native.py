@@ -105,8 +105,8 @@ def _load():
         "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, I, I, F, I, I, P]),
         "b2tts_short_conv_act": (I, [P, L, I, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, P]),
         "b2tts_gated_group_norm": (I, [P, P, L, P, I, I, I, I, F, P, I, I, I, P]),
-        "b2tts_ssm_scan": (I, [P, L, P, L, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
-        "b2tts_delta_rule_scan": (I, [P, L, P, P, L, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
+        "b2tts_ssm_scan": (I, [P, L, P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
+        "b2tts_delta_rule_scan": (I, [P, L, P, P, L, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
         "b2tts_matrix_memory_scan": (I, [P, P, P, P, P, L, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, P]),
         "b2tts_grouped_gemm": (I, [P, L, P, P, L, P, P, I, I, I, I, I, I, I, I, I, P]),
     }
@@ -994,8 +994,13 @@ def gated_group_norm(y, gate, w, groups, gate_act, gate_first, eps, out):
            "gated_group_norm")
 
 
-def _seq_args(lay):
-    return (lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(), lay.seq_slot.data_ptr(), lay.n_seqs)
+def _seq_args(lay, tokens=False):
+    head = (lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(), lay.seq_slot.data_ptr())
+    return head + ((lay.n_tokens, lay.n_seqs) if tokens else (lay.n_seqs,))
+
+
+def _coef(out, heads):
+    return torch.empty(out.shape[0], heads, 3, dtype=F32, device=out.device)
 
 
 def ssm_scan(xbc, dt_in, dt_bias, a_log, d_skip, state, out, lay, heads, groups, vdim, nstate):
@@ -1005,8 +1010,8 @@ def ssm_scan(xbc, dt_in, dt_bias, a_log, d_skip, state, out, lay, heads, groups,
     _cuda(state, F32, "state"); _cuda(out, F32, "out")
     assert dt_in.dtype == xbc.dtype and dt_in.stride(1) == 1 and state.is_contiguous() and out.is_contiguous()
     _check(_load().b2tts_ssm_scan(xbc.data_ptr(), xbc.stride(0), dt_in.data_ptr(), dt_in.stride(0), dt_bias.data_ptr(), a_log.data_ptr(),
-                                  d_skip.data_ptr(), state.data_ptr(), out.data_ptr(), *_seq_args(lay), heads, groups, vdim, nstate,
-                                  dt, _stream()), "ssm_scan")
+                                  d_skip.data_ptr(), state.data_ptr(), _coef(out, heads).data_ptr(), out.data_ptr(),
+                                  *_seq_args(lay, True), heads, groups, vdim, nstate, dt, _stream()), "ssm_scan")
 
 
 def delta_rule_scan(qkv, beta_in, a_in, a_log, dt_bias, state, out, lay, heads, kv_heads, dim, vdim):
@@ -1016,8 +1021,9 @@ def delta_rule_scan(qkv, beta_in, a_in, a_log, dt_bias, state, out, lay, heads, 
     assert beta_in.dtype == qkv.dtype and a_in.dtype == qkv.dtype and beta_in.stride(0) == a_in.stride(0)
     assert state.is_contiguous() and out.is_contiguous()
     _check(_load().b2tts_delta_rule_scan(qkv.data_ptr(), qkv.stride(0), beta_in.data_ptr(), a_in.data_ptr(), beta_in.stride(0),
-                                         a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), out.data_ptr(), *_seq_args(lay),
-                                         heads, kv_heads, dim, vdim, dt, _stream()), "delta_rule_scan")
+                                         a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), _coef(out, heads).data_ptr(),
+                                         out.data_ptr(), *_seq_args(lay, True), heads, kv_heads, dim, vdim, dt, _stream()),
+           "delta_rule_scan")
 
 
 def matrix_memory_scan(q, k, v, ig, fg, i_bias, f_bias, cap, state, state_nm, gates, out, lay, heads, dim, vdim):

@@ -5,10 +5,12 @@
 //                    with log gates i, f and the running maximum m = max(f + m, i), a = exp(f + m_old - m), b = exp(i - m)
 //   delta rule       S <- g S;  u = beta (v - S^T k);  S <- S + k u^T      o = S^T q
 //
-// All three update every value column of S independently, so one CTA owns up to 128 columns of one (sequence, head): the
-// columns' state lives in shared memory for the whole portion (column-major, one thread per column, conflict-free), the
-// per-token vectors (k, q or B, C) are staged in shared memory by all threads one token ahead of their use, and the
-// tokens of the portion are walked in order.  A decode step is the same kernel with one token.  The state is read from the
+// All three update every value column of S independently.  A column is shared by RS = ceil(key size / 32) lanes of one
+// warp, each keeping 32 rows of it in registers for the whole portion; sums over the rows (the read-out, the delta rule's
+// S^T k, the unit norms) are butterfly shuffles over those lanes.  The per-token vectors (k, q or B, C) are staged in
+// shared memory one element per thread (one barrier per token), their loads run four tokens ahead through registers, and
+// the tokens of the portion are walked in order.  What a token contributes besides its vectors - decay, step size, write
+// strength - depends on the inputs only and is computed for all tokens at once by a kernel in front.  A decode step is the same kernel with one token.  The state is read from the
 // sequence's slot (or starts at zero when the portion starts at position 0: a slot is never cleared between owners) and
 // written back at the end.  State, decays, gates, step sizes and unit norms are float whatever the activation type.
 //
@@ -22,205 +24,264 @@
 namespace b2 {
 namespace row {
 
-constexpr int SCAN_MAX_COLS = 128;
-constexpr int SCAN_PER = 8;               // vector elements a thread stages per token: key sizes up to 8 * blockDim
+constexpr int SCAN_ROWS = 32;             // state rows a thread keeps in registers
+constexpr int SCAN_COLS = 32;             // value columns per CTA
+constexpr int SCAN_PER = 8;               // key elements per lane of the one-warp gate kernel: key sizes up to 256
+constexpr int SCAN_DEPTH = 4;             // tokens whose inputs are in flight in registers
 
-enum { SCAN_SSM = 0, SCAN_MATRIX = 1, SCAN_DELTA = 2 };
+enum { SCAN_LINEAR = 0, SCAN_DELTA = 1 };
 
 struct ScanArgs {
   const void* k; int64_t ldk;             // key-like vectors: (row, group g, i) at k[row * ldk + g * d + i]
   const void* q; int64_t ldq;             // query-like vectors, same layout
   const void* v; int64_t ldv;             // values: (row, head h, c) at v[row * ldv + h * dv + c]
-  const void* s1; const void* s2; int64_t lds;   // per-head pre-activations: (row, h) at s[row * lds + h]
-  const float* f1; const float* f2; const float* f3;   // per-head constants
-  const float* gates;                     // matrix memory: [rows, H, 3] = (a, b, denominator)
+  const float* coef;                      // [rows, H, 3] per-token scalars, see scan_kernel
+  const float* skip;                      // [H] or null: out += skip[h] * value
   float* state;                           // [slots, H, d, dv]
   float* out;                             // [rows, H * dv]
   const int32_t* seq_start; const int32_t* seq_pos0; const int32_t* seq_len; const int32_t* seq_slot;
   int H, G, d, dv;
   float qscale;
+  int divide;                             // linear: out = S^T q * qscale / coef[2] instead of S^T q * qscale
 };
 
-template <typename T, int KIND>
-__global__ void __launch_bounds__(SCAN_MAX_COLS)
+// sum over the RS lanes that share a column (lane = slice * (32 / RS) + column): every one of them gets the total
+template <int RS>
+__device__ __forceinline__ float slice_sum(float v) {
+#pragma unroll
+  for (int o = 16; o >= 32 / RS; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Per-token scalars c = coef[row, h, :], computed beforehand (they depend on the inputs only, not on the state):
+//   SCAN_LINEAR   S <- c0 S + k (c1 v)^T;                               out = S^T q * qscale [/ c2] [+ skip v]
+//   SCAN_DELTA    S <- c0 S; u = c1 (v - S^T k^); S <- S + k^ u^T;      out = S^T q^ * qscale      (k^, q^: unit vectors)
+// RS = threads per value column = ceil(d / 32) rounded up to a power of two; the CTA is RS warps and owns 32 columns.  A
+// warp holds 32 / RS columns; thread (slice, column) keeps rows slice * 32 .. + 31 of its column in registers for the
+// whole portion.  Thread i stages element i of the token's k and q (zero beyond d) in shared memory; the loads run
+// SCAN_DEPTH tokens ahead through registers, so a token waits for the barrier and its own arithmetic only.
+template <typename T, int KIND, int RS>
+__global__ void __launch_bounds__(32 * RS)
 scan_kernel(const ScanArgs a) {
-  extern __shared__ float smem[];
-  __shared__ float red[33];
-  const int b = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * SCAN_MAX_COLS;
+  constexpr int CW = 32 / RS;                              // columns per warp
+  constexpr int DP = RS * SCAN_ROWS;                       // padded key size = threads
+  __shared__ __align__(16) float vec[2][2][DP];            // [buffer][k | q][row]
+  const int b = blockIdx.z, h = blockIdx.y;
   const int len = a.seq_len[b];
   if (len <= 0) return;
   const int d = a.d, dv = a.dv, H = a.H;
-  const int cols = min(SCAN_MAX_COLS, dv - c0);
   const int g = h / (H / a.G);
   const int start = a.seq_start[b], pos0 = a.seq_pos0[b];
-  const int tid = threadIdx.x, nt = blockDim.x;
-  float* S = smem;                                        // [d][cols]
-  float* vec = smem + static_cast<size_t>(d) * cols;      // 2 x (k [d] | q [d])
-  float* Sg = a.state + (static_cast<size_t>(a.seq_slot[b]) * H + h) * d * dv + c0;
-  if (tid < cols) {
-    if (pos0 == 0) for (int i = 0; i < d; ++i) S[i * cols + tid] = 0.f;
-    else for (int i = 0; i < d; ++i) S[i * cols + tid] = Sg[static_cast<size_t>(i) * dv + tid];
-  }
-  const T* kp = static_cast<const T*>(a.k) + g * d;
-  const T* qp = static_cast<const T*>(a.q) + g * d;
-  const T* vp = static_cast<const T*>(a.v) + h * dv + c0;
-  const T* s1 = static_cast<const T*>(a.s1);
-  const T* s2 = static_cast<const T*>(a.s2);
-  float c_f1 = 0.f, c_f2 = 0.f, c_f3 = 0.f;
-  if (a.f1 != nullptr) c_f1 = a.f1[h];
-  if (a.f2 != nullptr) c_f2 = a.f2[h];
-  if (a.f3 != nullptr) c_f3 = a.f3[h];
-
-  // registers holding the NEXT token's inputs
-  float rk[SCAN_PER], rq[SCAN_PER], rv = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
-  auto fetch = [&](int t) {
-    const size_t r = static_cast<size_t>(start + t);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int slice = lane / CW;
+  const int col = blockIdx.x * SCAN_COLS + warp * CW + (lane % CW);
+  const bool live = col < dv, mine = tid < d;
+  const int r0 = slice * SCAN_ROWS;
+  float S[SCAN_ROWS];
+  float* Sg = a.state + ((static_cast<size_t>(a.seq_slot[b]) * H + h) * d) * dv + col;
 #pragma unroll
-    for (int x = 0; x < SCAN_PER; ++x) {
-      const int i = tid + x * nt;
-      if (i < d) { rk[x] = to_f(kp[r * a.ldk + i]); rq[x] = to_f(qp[r * a.ldq + i]); }
-    }
-    if (tid < cols) rv = to_f(vp[r * a.ldv + tid]);
-    if constexpr (KIND == SCAN_SSM) r1 = to_f(s1[r * a.lds + h]);
-    if constexpr (KIND == SCAN_DELTA) { r1 = to_f(s1[r * a.lds + h]); r2 = to_f(s2[r * a.lds + h]); }
-    if constexpr (KIND == SCAN_MATRIX) {
-      const float* gp = a.gates + (r * H + h) * 3;
-      r1 = gp[0]; r2 = gp[1]; r3 = gp[2];
+  for (int x = 0; x < SCAN_ROWS; ++x) {
+    const int i = r0 + x;
+    S[x] = (live && pos0 > 0 && i < d) ? Sg[static_cast<size_t>(i) * dv] : 0.f;
+  }
+  const T* kp = static_cast<const T*>(a.k) + static_cast<size_t>(start) * a.ldk + g * d + tid;
+  const T* qp = static_cast<const T*>(a.q) + static_cast<size_t>(start) * a.ldq + g * d + tid;
+  const T* vp = static_cast<const T*>(a.v) + static_cast<size_t>(start) * a.ldv + h * dv + col;
+  const float* cp = a.coef + (static_cast<size_t>(start) * H + h) * 3;
+  float* op = a.out + static_cast<size_t>(start) * H * dv + h * dv + col;
+  const float skip = a.skip != nullptr ? a.skip[h] : 0.f;
+
+  // the loaded values stay as they came (type T) until their token is staged: converting them at once would make the
+  // thread wait for the load, four tokens early
+  T rk[SCAN_DEPTH], rq[SCAN_DEPTH], rv[SCAN_DEPTH];
+  float rc[SCAN_DEPTH][3];
+  auto fetch = [&](int u, int t) {                         // token t's inputs into register stage u
+    rk[u] = rq[u] = rv[u] = from_f<T>(0.f);
+    rc[u][0] = rc[u][1] = 0.f; rc[u][2] = 1.f;
+    if (t < len) {
+      if (mine) { rk[u] = kp[static_cast<size_t>(t) * a.ldk]; rq[u] = qp[static_cast<size_t>(t) * a.ldq]; }
+      if (live) rv[u] = vp[static_cast<size_t>(t) * a.ldv];
+      const float* c = cp + static_cast<size_t>(t) * H * 3;
+      rc[u][0] = c[0]; rc[u][1] = c[1]; rc[u][2] = c[2];
     }
   };
-  fetch(0);
-  for (int t = 0; t < len; ++t) {
-    float* ks = vec + (t & 1) * 2 * d;
-    float* qs = ks + d;
-    float ssk = 0.f, ssq = 0.f;
 #pragma unroll
-    for (int x = 0; x < SCAN_PER; ++x) {
-      const int i = tid + x * nt;
-      if (i < d) { ks[i] = rk[x]; qs[i] = rq[x]; ssk += rk[x] * rk[x]; ssq += rq[x] * rq[x]; }
-    }
-    const float val = rv, p1 = r1, p2 = r2, p3 = r3;
-    if (t + 1 < len) fetch(t + 1);
-    float kn = 1.f, qn = a.qscale;
-    if constexpr (KIND == SCAN_DELTA) {                   // unit vectors; the block sums also publish ks / qs
-      kn = 1.0f / sqrtf(block_sum(ssk, red) + 1e-6f);
-      qn = a.qscale / sqrtf(block_sum(ssq, red) + 1e-6f);
-    } else {
-      __syncthreads();
-    }
-    if (tid < cols) {
-      float o = 0.f;
-      if constexpr (KIND == SCAN_SSM) {
-        const float dt = softplus_f(p1 + c_f1);
-        const float dA = expf(-expf(c_f2) * dt);
-        const float w = dt * val;
-        for (int i = 0; i < d; ++i) {
-          const float s = dA * S[i * cols + tid] + ks[i] * w;
-          S[i * cols + tid] = s;
-          o += s * qs[i];
-        }
-        o += c_f3 * val;
-      } else if constexpr (KIND == SCAN_MATRIX) {
-        const float w = p2 * val;
-        for (int i = 0; i < d; ++i) {
-          const float s = p1 * S[i * cols + tid] + ks[i] * w;
-          S[i * cols + tid] = s;
-          o += s * qs[i];
-        }
-        o = o * qn / p3;
-      } else {
-        const float beta = sigmoid_f(p1);
-        const float decay = expf(-expf(c_f1) * softplus_f(p2 + c_f2));
-        float kv = 0.f;
-        for (int i = 0; i < d; ++i) {
-          const float s = decay * S[i * cols + tid];
-          S[i * cols + tid] = s;
-          kv += s * (ks[i] * kn);
-        }
-        const float u = beta * (val - kv);
-        for (int i = 0; i < d; ++i) {
-          const float s = S[i * cols + tid] + (ks[i] * kn) * u;
-          S[i * cols + tid] = s;
-          o += s * (qs[i] * qn);
-        }
+  for (int u = 0; u < SCAN_DEPTH; ++u) fetch(u, u);
+  for (int t0 = 0; t0 < len; t0 += SCAN_DEPTH) {
+#pragma unroll
+    for (int u = 0; u < SCAN_DEPTH; ++u) {
+      const int t = t0 + u;
+      if (t >= len) break;                                 // uniform over the CTA
+      float* ks = vec[u & 1][0];
+      float* qs = vec[u & 1][1];
+      ks[tid] = to_f(rk[u]);
+      qs[tid] = to_f(rq[u]);
+      const float val = to_f(rv[u]), c0 = rc[u][0], c1 = rc[u][1], c2 = rc[u][2];
+      fetch(u, t + SCAN_DEPTH);
+      __syncthreads();                                     // token t is staged; the other buffer is free again
+      float kr[SCAN_ROWS];
+#pragma unroll
+      for (int x = 0; x < SCAN_ROWS; x += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + r0 + x);
+        kr[x] = k4.x; kr[x + 1] = k4.y; kr[x + 2] = k4.z; kr[x + 3] = k4.w;
       }
-      a.out[static_cast<size_t>(start + t) * H * dv + h * dv + c0 + tid] = o;
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f, o;
+      if constexpr (KIND == SCAN_LINEAR) {
+        const float w = c1 * val;
+#pragma unroll
+        for (int x = 0; x < SCAN_ROWS; x += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qs + r0 + x);
+          S[x] = c0 * S[x] + kr[x] * w;             o0 += S[x] * q4.x;
+          S[x + 1] = c0 * S[x + 1] + kr[x + 1] * w; o1 += S[x + 1] * q4.y;
+          S[x + 2] = c0 * S[x + 2] + kr[x + 2] * w; o2 += S[x + 2] * q4.z;
+          S[x + 3] = c0 * S[x + 3] + kr[x + 3] * w; o3 += S[x + 3] * q4.w;
+        }
+        o = slice_sum<RS>((o0 + o1) + (o2 + o3)) * a.qscale;
+        if (a.divide) o /= c2;
+        o += skip * val;
+      } else {
+        // unit vectors: every thread sums the squares of its slice, the slices of a column add up to the whole vector
+        float ssk = 0.f, ssq = 0.f, kv0 = 0.f, kv1 = 0.f;
+#pragma unroll
+        for (int x = 0; x < SCAN_ROWS; x += 2) {
+          ssk += kr[x] * kr[x] + kr[x + 1] * kr[x + 1];
+          S[x] *= c0;     kv0 += S[x] * kr[x];
+          S[x + 1] *= c0; kv1 += S[x + 1] * kr[x + 1];
+        }
+        const float kn = 1.0f / sqrtf(slice_sum<RS>(ssk) + 1e-6f);
+        const float kv = slice_sum<RS>(kv0 + kv1) * kn;
+        const float w = c1 * (val - kv) * kn;              // k^ u^T = k (kn u)^T
+#pragma unroll
+        for (int x = 0; x < SCAN_ROWS; x += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qs + r0 + x);
+          S[x] += kr[x] * w;         o0 += S[x] * q4.x;     ssq += q4.x * q4.x;
+          S[x + 1] += kr[x + 1] * w; o1 += S[x + 1] * q4.y; ssq += q4.y * q4.y;
+          S[x + 2] += kr[x + 2] * w; o2 += S[x + 2] * q4.z; ssq += q4.z * q4.z;
+          S[x + 3] += kr[x + 3] * w; o3 += S[x + 3] * q4.w; ssq += q4.w * q4.w;
+        }
+        o = slice_sum<RS>((o0 + o1) + (o2 + o3)) * (a.qscale / sqrtf(slice_sum<RS>(ssq) + 1e-6f));
+      }
+      if (live && slice == 0) op[static_cast<size_t>(t) * H * dv] = o;
     }
   }
-  if (tid < cols)
-    for (int i = 0; i < d; ++i) Sg[static_cast<size_t>(i) * dv + tid] = S[i * cols + tid];
+  if (live) {
+#pragma unroll
+    for (int x = 0; x < SCAN_ROWS; ++x) {
+      const int i = r0 + x;
+      if (i < d) Sg[static_cast<size_t>(i) * dv] = S[x];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ per-token scalars of the state space and the delta rule
+// kind 0: dt = softplus(s1 + f1[h]); coef = (exp(-exp(f2[h]) dt), dt, 1)                       (f1 = dt_bias, f2 = A_log)
+// kind 1: coef = (exp(-exp(f1[h]) softplus(s2 + f2[h])), sigmoid(s1), 1)                      (f1 = A_log, f2 = dt_bias)
+template <typename T>
+__global__ void scan_coef_kernel(const T* __restrict__ s1, const T* __restrict__ s2, int64_t lds, const float* __restrict__ f1,
+                                 const float* __restrict__ f2, float* __restrict__ coef, int n_tokens, int H, int kind) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_tokens * H) return;
+  const size_t t = idx / H;
+  const int h = idx % H;
+  float c0, c1;
+  if (kind == 0) {
+    const float dt = softplus_f(to_f(s1[t * lds + h]) + f1[h]);
+    c0 = expf(-expf(f2[h]) * dt);
+    c1 = dt;
+  } else {
+    c0 = expf(-expf(f1[h]) * softplus_f(to_f(s2[t * lds + h]) + f2[h]));
+    c1 = sigmoid_f(to_f(s1[t * lds + h]));
+  }
+  float* c = coef + static_cast<size_t>(idx) * 3;
+  c[0] = c0; c[1] = c1; c[2] = 1.f;
 }
 
 // ------------------------------------------------------------------ scalar part of the matrix memory
-// One CTA per (sequence, head).  i = cap tanh((ig + bi) / cap), f = logsigmoid(cap tanh((fg + bf) / cap));
+// One warp per (sequence, head).  i = cap tanh((ig + bi) / cap), f = logsigmoid(cap tanh((fg + bf) / cap));
 // m' = max(f + m, i), a = exp(f + m - m'), b = exp(i - m'); n <- a n + b k; den = max(|n . q * qscale|, exp(-m')) + 1e-6.
-// state_nm [slots, H, d + 1]: n, then m (m starts at 0).
+// state_nm [slots, H, d + 1]: n, then m (m starts at 0).  The next token's inputs are fetched while this one is computed.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32)
 matrix_memory_gates_kernel(const T* __restrict__ k, const T* __restrict__ q, const T* __restrict__ ig, const T* __restrict__ fg,
                            int64_t ldu, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
                            float qscale, float* __restrict__ state_nm, float* __restrict__ gates,
                            const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                            const int32_t* __restrict__ seq_len, const int32_t* __restrict__ seq_slot, int H, int d) {
-  __shared__ float red[33];
   const int b = blockIdx.y, h = blockIdx.x;
   const int len = seq_len[b];
   if (len <= 0) return;
-  const int start = seq_start[b], pos0 = seq_pos0[b], tid = threadIdx.x, nt = blockDim.x;
+  const int start = seq_start[b], pos0 = seq_pos0[b], lane = threadIdx.x;
   float* nm = state_nm + (static_cast<size_t>(seq_slot[b]) * H + h) * (d + 1);
   float n[SCAN_PER];
+  T rk[SCAN_PER], rq[SCAN_PER], ri, rf;                    // the next token's inputs, converted only when they are used
 #pragma unroll
   for (int x = 0; x < SCAN_PER; ++x) {
-    const int i = tid + x * nt;
+    const int i = lane + x * 32;
     n[x] = (i < d && pos0 > 0) ? nm[i] : 0.f;
   }
   float m = pos0 > 0 ? nm[d] : 0.f;
   const float bi = i_bias[h], bf = f_bias[h];
-  for (int t = 0; t < len; ++t) {
+  auto fetch = [&](int t) {
     const size_t r = static_cast<size_t>(start + t);
-    const float li = cap * tanhf((to_f(ig[r * ldu + h]) + bi) / cap);
-    const float lf = logsigmoid_f(cap * tanhf((to_f(fg[r * ldu + h]) + bf) / cap));
+#pragma unroll
+    for (int x = 0; x < SCAN_PER; ++x) {
+      const int i = lane + x * 32;
+      rk[x] = rq[x] = from_f<T>(0.f);
+      if (i < d) { rk[x] = k[r * ldu + h * d + i]; rq[x] = q[r * ldu + h * d + i]; }
+    }
+    ri = ig[r * ldu + h];
+    rf = fg[r * ldu + h];
+  };
+  fetch(0);
+  for (int t = 0; t < len; ++t) {
+    const float li = cap * tanhf((to_f(ri) + bi) / cap);
+    const float lf = logsigmoid_f(cap * tanhf((to_f(rf) + bf) / cap));
     const float m_new = fmaxf(lf + m, li);
     const float ca = expf(lf + m - m_new), cb = expf(li - m_new);
     m = m_new;
     float nq = 0.f;
 #pragma unroll
     for (int x = 0; x < SCAN_PER; ++x) {
-      const int i = tid + x * nt;
-      if (i < d) {
-        n[x] = ca * n[x] + cb * to_f(k[r * ldu + h * d + i]);
-        nq += n[x] * (to_f(q[r * ldu + h * d + i]) * qscale);
-      }
+      n[x] = ca * n[x] + cb * to_f(rk[x]);
+      nq += n[x] * (to_f(rq[x]) * qscale);
     }
-    nq = block_sum(nq, red);
-    if (tid == 0) {
-      float* gp = gates + (r * H + h) * 3;
+    if (t + 1 < len) fetch(t + 1);
+    nq = warp_sum(nq);
+    if (lane == 0) {
+      float* gp = gates + (static_cast<size_t>(start + t) * H + h) * 3;
       gp[0] = ca; gp[1] = cb; gp[2] = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
     }
   }
 #pragma unroll
   for (int x = 0; x < SCAN_PER; ++x) {
-    const int i = tid + x * nt;
+    const int i = lane + x * 32;
     if (i < d) nm[i] = n[x];
   }
-  if (tid == 0) nm[d] = m;
+  if (lane == 0) nm[d] = m;
+}
+
+template <typename T, int KIND, int RS>
+static void launch_scan_rs(const ScanArgs& a, int n_seqs, cudaStream_t st) {
+  const dim3 grid((a.dv + SCAN_COLS - 1) / SCAN_COLS, a.H, n_seqs);
+  scan_kernel<T, KIND, RS><<<grid, 32 * RS, 0, st>>>(a);
 }
 
 template <typename T, int KIND>
 static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t st, const char* what) {
-  const int cols = std::min(SCAN_MAX_COLS, a.dv);
-  const int threads = std::max(32, (cols + 31) / 32 * 32);
-  B2_REQUIRE(a.d <= SCAN_PER * threads, B2TTS_EUNSUPPORTED, "%s: key size %d above %d", what, a.d, SCAN_PER * threads);
-  const size_t sm = (static_cast<size_t>(a.d) * cols + 4 * static_cast<size_t>(a.d)) * sizeof(float);
-  B2_REQUIRE(sm <= 220 * 1024, B2TTS_EUNSUPPORTED, "%s: %d x %d columns of state do not fit shared memory", what, a.d, cols);
-  static size_t opted = 0;                               // per instantiation
-  if (sm > 48 * 1024 && sm > opted) {
-    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm));
-    if (e != cudaSuccess) return cuda_fail(e, what);
-    opted = sm;
-  }
-  const dim3 grid((a.dv + SCAN_MAX_COLS - 1) / SCAN_MAX_COLS, a.H, n_seqs);
-  scan_kernel<T, KIND><<<grid, threads, sm, st>>>(a);
+  B2_REQUIRE(a.d <= 8 * SCAN_ROWS, B2TTS_EUNSUPPORTED, "%s: key size %d above %d", what, a.d, 8 * SCAN_ROWS);
+  if (a.d <= 32) launch_scan_rs<T, KIND, 1>(a, n_seqs, st);
+  else if (a.d <= 64) launch_scan_rs<T, KIND, 2>(a, n_seqs, st);
+  else if (a.d <= 128) launch_scan_rs<T, KIND, 4>(a, n_seqs, st);
+  else launch_scan_rs<T, KIND, 8>(a, n_seqs, st);
   return B2TTS_OK;
+}
+
+template <typename T>
+static void launch_coef(const void* s1, const void* s2, int64_t lds, const float* f1, const float* f2, float* coef, int n_tokens, int H,
+                        int kind, cudaStream_t st) {
+  const int total = n_tokens * H;
+  scan_coef_kernel<T><<<(total + 255) / 256, 256, 0, st>>>(static_cast<const T*>(s1), static_cast<const T*>(s2), lds, f1, f2, coef,
+                                                          n_tokens, H, kind);
 }
 
 }  // namespace row
@@ -237,53 +298,59 @@ using namespace b2::row;
   B2_REQUIRE(state && out && seq_start && seq_pos0 && seq_len && seq_slot, B2TTS_EINVAL, name ": null pointer")
 
 extern "C" int b2tts_ssm_scan(const void* xbc, int64_t ldx, const void* dt, int64_t lddt, const float* dt_bias,
-                              const float* a_log, const float* d_skip, float* state, float* out, const int32_t* seq_start,
-                              const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot, int n_seqs, int heads,
-                              int groups, int vdim, int dim, int dtype, void* stream) {
+                              const float* a_log, const float* d_skip, float* state, float* coef, float* out, const int32_t* seq_start,
+                              const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot, int n_tokens, int n_seqs,
+                              int heads, int groups, int vdim, int dim, int dtype, void* stream) {
   SCAN_COMMON_CHECKS("ssm_scan");
-  B2_REQUIRE(groups > 0 && heads % groups == 0, B2TTS_EINVAL, "ssm_scan: %d heads over %d groups", heads, groups);
-  B2_REQUIRE(xbc && dt && dt_bias && a_log && d_skip, B2TTS_EINVAL, "ssm_scan: null pointer");
+  B2_REQUIRE(groups > 0 && heads % groups == 0 && n_tokens >= 0, B2TTS_EINVAL, "ssm_scan: %d heads over %d groups", heads, groups);
+  B2_REQUIRE(xbc && dt && dt_bias && a_log && d_skip && coef, B2TTS_EINVAL, "ssm_scan: null pointer");
+  if (n_tokens == 0) return B2TTS_OK;
   const size_t el = dtype == B2TTS_DTYPE_BF16 ? 2 : 4;
   const int inner = heads * vdim;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B2TTS_DTYPE_BF16) launch_coef<__nv_bfloat16>(dt, nullptr, lddt, dt_bias, a_log, coef, n_tokens, heads, 0, st);
+  else launch_coef<float>(dt, nullptr, lddt, dt_bias, a_log, coef, n_tokens, heads, 0, st);
+  B2_CHECK_LAUNCH("ssm_scan (scalars)");
   ScanArgs a{};
   const char* base = static_cast<const char*>(xbc);
   a.v = base; a.ldv = ldx;
   a.k = base + static_cast<size_t>(inner) * el; a.ldk = ldx;
   a.q = base + (static_cast<size_t>(inner) + static_cast<size_t>(groups) * dim) * el; a.ldq = ldx;
-  a.s1 = dt; a.lds = lddt;
-  a.f1 = dt_bias; a.f2 = a_log; a.f3 = d_skip;
+  a.coef = coef; a.skip = d_skip;
   a.state = state; a.out = out;
   a.seq_start = seq_start; a.seq_pos0 = seq_pos0; a.seq_len = seq_len; a.seq_slot = seq_slot;
-  a.H = heads; a.G = groups; a.d = dim; a.dv = vdim; a.qscale = 1.f;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int rc = dtype == B2TTS_DTYPE_BF16 ? launch_scan<__nv_bfloat16, SCAN_SSM>(a, n_seqs, st, "ssm_scan")
-                                           : launch_scan<float, SCAN_SSM>(a, n_seqs, st, "ssm_scan");
+  a.H = heads; a.G = groups; a.d = dim; a.dv = vdim; a.qscale = 1.f; a.divide = 0;
+  const int rc = dtype == B2TTS_DTYPE_BF16 ? launch_scan<__nv_bfloat16, SCAN_LINEAR>(a, n_seqs, st, "ssm_scan")
+                                           : launch_scan<float, SCAN_LINEAR>(a, n_seqs, st, "ssm_scan");
   if (rc != B2TTS_OK) return rc;
   B2_CHECK_LAUNCH("ssm_scan");
   return B2TTS_OK;
 }
 
 extern "C" int b2tts_delta_rule_scan(const void* qkv, int64_t ldq, const void* beta, const void* a_in, int64_t ldu,
-                                     const float* a_log, const float* dt_bias, float* state, float* out,
+                                     const float* a_log, const float* dt_bias, float* state, float* coef, float* out,
                                      const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
-                                     const int32_t* seq_slot, int n_seqs, int heads, int kv_heads, int dim, int vdim, int dtype,
-                                     void* stream) {
+                                     const int32_t* seq_slot, int n_tokens, int n_seqs, int heads, int kv_heads, int dim, int vdim,
+                                     int dtype, void* stream) {
   SCAN_COMMON_CHECKS("delta_rule_scan");
-  B2_REQUIRE(kv_heads > 0 && heads % kv_heads == 0, B2TTS_EINVAL, "delta_rule_scan: %d heads over %d key heads", heads, kv_heads);
-  B2_REQUIRE(qkv && beta && a_in && a_log && dt_bias, B2TTS_EINVAL, "delta_rule_scan: null pointer");
+  B2_REQUIRE(kv_heads > 0 && heads % kv_heads == 0 && n_tokens >= 0, B2TTS_EINVAL, "delta_rule_scan: %d heads over %d key heads", heads, kv_heads);
+  B2_REQUIRE(qkv && beta && a_in && a_log && dt_bias && coef, B2TTS_EINVAL, "delta_rule_scan: null pointer");
+  if (n_tokens == 0) return B2TTS_OK;
   const size_t el = dtype == B2TTS_DTYPE_BF16 ? 2 : 4;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B2TTS_DTYPE_BF16) launch_coef<__nv_bfloat16>(beta, a_in, ldu, a_log, dt_bias, coef, n_tokens, heads, 1, st);
+  else launch_coef<float>(beta, a_in, ldu, a_log, dt_bias, coef, n_tokens, heads, 1, st);
+  B2_CHECK_LAUNCH("delta_rule_scan (scalars)");
   ScanArgs a{};
   const char* base = static_cast<const char*>(qkv);
   const size_t gd = static_cast<size_t>(kv_heads) * dim;
   a.q = base; a.ldq = ldq;
   a.k = base + gd * el; a.ldk = ldq;
   a.v = base + 2 * gd * el; a.ldv = ldq;
-  a.s1 = beta; a.s2 = a_in; a.lds = ldu;
-  a.f1 = a_log; a.f2 = dt_bias;
+  a.coef = coef;
   a.state = state; a.out = out;
   a.seq_start = seq_start; a.seq_pos0 = seq_pos0; a.seq_len = seq_len; a.seq_slot = seq_slot;
-  a.H = heads; a.G = kv_heads; a.d = dim; a.dv = vdim; a.qscale = 1.0f / sqrtf(static_cast<float>(dim));
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  a.H = heads; a.G = kv_heads; a.d = dim; a.dv = vdim; a.qscale = 1.0f / sqrtf(static_cast<float>(dim)); a.divide = 0;
   const int rc = dtype == B2TTS_DTYPE_BF16 ? launch_scan<__nv_bfloat16, SCAN_DELTA>(a, n_seqs, st, "delta_rule_scan")
                                            : launch_scan<float, SCAN_DELTA>(a, n_seqs, st, "delta_rule_scan");
   if (rc != B2TTS_OK) return rc;
@@ -299,11 +366,11 @@ extern "C" int b2tts_matrix_memory_scan(const void* q, const void* k, const void
   SCAN_COMMON_CHECKS("matrix_memory_scan");
   B2_REQUIRE(q && k && v && ig && fg && i_bias && f_bias && state_nm && gates && cap > 0.f, B2TTS_EINVAL,
              "matrix_memory_scan: null pointer or cap <= 0");
-  B2_REQUIRE(dim <= SCAN_PER * 128, B2TTS_EUNSUPPORTED, "matrix_memory_scan: key size %d above %d", dim, SCAN_PER * 128);
+  B2_REQUIRE(dim <= SCAN_PER * 32, B2TTS_EUNSUPPORTED, "matrix_memory_scan: key size %d above %d", dim, SCAN_PER * 32);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const float qscale = 1.0f / sqrtf(static_cast<float>(dim));
   const dim3 ggrid(heads, n_seqs);
-  const int gthreads = std::min(128, std::max(32, (dim + 31) / 32 * 32));
+  const int gthreads = 32;
   if (dtype == B2TTS_DTYPE_BF16)
     matrix_memory_gates_kernel<__nv_bfloat16><<<ggrid, gthreads, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(ig), static_cast<const __nv_bfloat16*>(fg), ldu, i_bias,
@@ -315,12 +382,12 @@ extern "C" int b2tts_matrix_memory_scan(const void* q, const void* k, const void
   B2_CHECK_LAUNCH("matrix_memory_gates");
   ScanArgs a{};
   a.q = q; a.ldq = ldu; a.k = k; a.ldk = ldu; a.v = v; a.ldv = ldu;
-  a.gates = gates;
+  a.coef = gates; a.divide = 1;
   a.state = state; a.out = out;
   a.seq_start = seq_start; a.seq_pos0 = seq_pos0; a.seq_len = seq_len; a.seq_slot = seq_slot;
   a.H = heads; a.G = heads; a.d = dim; a.dv = vdim; a.qscale = qscale;
-  const int rc = dtype == B2TTS_DTYPE_BF16 ? launch_scan<__nv_bfloat16, SCAN_MATRIX>(a, n_seqs, st, "matrix_memory_scan")
-                                           : launch_scan<float, SCAN_MATRIX>(a, n_seqs, st, "matrix_memory_scan");
+  const int rc = dtype == B2TTS_DTYPE_BF16 ? launch_scan<__nv_bfloat16, SCAN_LINEAR>(a, n_seqs, st, "matrix_memory_scan")
+                                           : launch_scan<float, SCAN_LINEAR>(a, n_seqs, st, "matrix_memory_scan");
   if (rc != B2TTS_OK) return rc;
   B2_CHECK_LAUNCH("matrix_memory_scan");
   return B2TTS_OK;

@@ -46,6 +46,31 @@ __device__ __forceinline__ float dot_row(const T* __restrict__ kr, const float* 
   return acc;
 }
 
+// `cpl` consecutive value columns of one cached row -> floats; `bytes` = cpl * sizeof(T) when the row allows vector loads, else 0
+template <typename T>
+__device__ __forceinline__ void load_cols(const T* __restrict__ p, int cpl, int bytes, int room, float* f) {
+  if (bytes == 0) {
+#pragma unroll
+    for (int x = 0; x < SA_MAX_PER_LANE; ++x) f[x] = (x < cpl && x < room) ? to_f(p[x]) : 0.f;
+    return;
+  }
+  uint32_t w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (bytes == 4) w[0] = *reinterpret_cast<const uint32_t*>(p);
+  else if (bytes == 8) { const uint2 r = ldg_v2(p); w[0] = r.x; w[1] = r.y; }
+  else {
+    const uint4 r = ldg_v4(p);
+    w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
+    if (bytes == 32) { const uint4 r2 = ldg_v4(reinterpret_cast<const char*>(p) + 16); w[4] = r2.x; w[5] = r2.y; w[6] = r2.z; w[7] = r2.w; }
+  }
+  if constexpr (sizeof(T) == 2) {
+#pragma unroll
+    for (int x = 0; x < 4; ++x) { f[2 * x] = bf16lo(w[x]); f[2 * x + 1] = bf16hi(w[x]); }
+  } else {
+#pragma unroll
+    for (int x = 0; x < 8; ++x) f[x] = __uint_as_float(w[x]);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SA_WARPS * 32)
 sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
@@ -75,6 +100,11 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
   const int32_t* bt = block_tables + static_cast<int64_t>(b) * bt_stride;
   const int nk = G * d, nv = G * dv;
   const bool vec = (d % Vec16<T>::N) == 0;            // rows then start on 16-byte boundaries (the cache base is aligned)
+  // a lane owns `cpl` consecutive value columns; with dv a multiple of 32 they are one aligned vector load per key
+  const int cpl = (dv + 31) / 32, c_lane = lane * cpl;
+  const int cbytes = cpl * static_cast<int>(sizeof(T));
+  const int vbytes = (dv % 32 == 0 && (cbytes == 4 || cbytes == 8 || cbytes == 16 || cbytes == 32)) ? cbytes : 0;
+  const int room = max(0, min(cpl, dv - c_lane));
   float m = -INFINITY, l = 0.f;
   float acc[SA_MAX_PER_LANE];
 #pragma unroll
@@ -99,20 +129,16 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
     for (int kk = 0; kk < cnt; ++kk) {
       const float pk = __shfl_sync(0xffffffffu, p, kk);
       const int sk = __shfl_sync(0xffffffffu, slot, kk);
-      const T* vr = v_cache + static_cast<size_t>(sk) * nv + g * dv;
+      float vf[SA_MAX_PER_LANE];
+      load_cols<T>(v_cache + static_cast<size_t>(sk) * nv + g * dv + (room > 0 ? c_lane : 0), cpl, vbytes, room, vf);
 #pragma unroll
-      for (int x = 0; x < SA_MAX_PER_LANE; ++x) {
-        const int c = lane + 32 * x;
-        if (c < dv) acc[x] += pk * to_f(vr[c]);
-      }
+      for (int x = 0; x < SA_MAX_PER_LANE; ++x) acc[x] += pk * vf[x];
     }
   }
   float* mine = part + warp * (dv + 2);
 #pragma unroll
-  for (int x = 0; x < SA_MAX_PER_LANE; ++x) {
-    const int c = lane + 32 * x;
-    if (c < dv) mine[c] = acc[x];
-  }
+  for (int x = 0; x < SA_MAX_PER_LANE; ++x)
+    if (x < room) mine[c_lane + x] = acc[x];
   if (lane == 0) { mine[dv] = m; mine[dv + 1] = l; }
   __syncthreads();
   const float sk = sink != nullptr ? sink[h] : -INFINITY;
