@@ -558,11 +558,11 @@ B2TTS_API int b2tts_sink_attn(const void* q, const void* k_cache, const void* v_
                               int mask_kind, int mask, float scale, int dtype, int path, void* stream);
 /* out[t, c] = act(bias[c] + sum_j w[c, j] * u(position(t) - taps + 1 + j)[c_off + c]) for c < channels (act 0: none, 1: SiLU;
  * bias may be null).  Earlier positions come from this step's rows, from state [slots, taps-1, channels] (the sequence's last
- * rows, oldest first, advanced by this call) or are zero before position 0. */
+ * rows, oldest first, advanced by this call) or are zero before position 0.  max_new >= every seq_len[b] (0: unknown). */
 B2TTS_API int b2tts_short_conv_act(const void* u, int64_t ldu, int c_off, const float* w, const float* bias, void* state,
                                    const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_start,
                                    const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot, void* out, int64_t ldo,
-                                   int n_tokens, int n_seqs, int channels, int taps, int act, int dtype, void* stream);
+                                   int n_tokens, int n_seqs, int max_new, int channels, int taps, int act, int dtype, void* stream);
 /* Row y [cols] (float) in `groups` equal parts, each divided by its root mean square, times w[c mod w_len]; the gate
  * (sigmoid for gate_act 0, SiLU for 1, of gate[r * ldg + c]; null: none) multiplies y before the norm (gate_first) or after. */
 B2TTS_API int b2tts_gated_group_norm(const float* y, const void* gate, int64_t ldg, const float* w, int w_len, int groups,

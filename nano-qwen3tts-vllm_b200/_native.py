@@ -103,7 +103,7 @@ def _load():
         "b2tts_stream_gather_norm": (I, [P, P, P, P, P, I, I, I, F, I, P]),
         "b2tts_attn_prep": (I, [P, L, I, I, I, P, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, P]),
         "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, I, I, F, I, I, P]),
-        "b2tts_short_conv_act": (I, [P, L, I, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, P]),
+        "b2tts_short_conv_act": (I, [P, L, I, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, I, P]),
         "b2tts_gated_group_norm": (I, [P, P, L, P, I, I, I, I, F, P, I, I, I, P]),
         "b2tts_ssm_scan": (I, [P, L, P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
         "b2tts_delta_rule_scan": (I, [P, L, P, P, L, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
@@ -978,7 +978,7 @@ def short_conv_act(u, c_off, channels, w, bias, state, lay, out, taps, act=1):
     _check(_load().b2tts_short_conv_act(u.data_ptr(), u.stride(0), c_off, w.data_ptr(), _ptr(bias), _ptr(state), lay.tok_seq.data_ptr(),
                                         lay.positions.data_ptr(), lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(),
                                         lay.seq_len.data_ptr(), lay.seq_slot.data_ptr(), out.data_ptr(), out.stride(0), lay.n_tokens,
-                                        lay.n_seqs, channels, taps, act, dt, _stream()), "short_conv_act")
+                                        lay.n_seqs, lay.max_new, channels, taps, act, dt, _stream()), "short_conv_act")
 
 
 GATE_SIGMOID, GATE_SILU = 0, 1

@@ -99,6 +99,101 @@ stream_mix_norm_kernel(float* __restrict__ xs, const T* __restrict__ y1, const T
   }
 }
 
+// four consecutive activations <-> floats (16-byte loads for float, 8-byte for bf16); p must be aligned accordingly
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 r = ldg_v2(p);
+  return make_float4(bf16lo(r.x), bf16hi(r.x), bf16lo(r.y), bf16hi(r.y));
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  stg_v2(p, make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w)));
+}
+
+// The same update and read-out for rows of cols % 4 == 0 and cols <= 4 * SMV_KEEP * ROW_THREADS: a thread owns groups of
+// four consecutive columns, moves them as vectors and keeps its read-out values in registers for the norm, so the
+// streams are read once and written once.
+constexpr int SMV_KEEP = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+stream_mix_norm_vec4_kernel(float* __restrict__ xs, const T* __restrict__ y1, const T* __restrict__ y2, float c1, float c2,
+                            const float* __restrict__ mix, const float* __restrict__ out_w, const float* __restrict__ in_w,
+                            const float* __restrict__ norm_w, T* __restrict__ h, int cols, int streams, float eps) {
+  __shared__ float red[33];
+  __shared__ float s_mix[MAX_STREAMS * MAX_STREAMS], s_out[MAX_STREAMS], s_in[MAX_STREAMS];
+  if (threadIdx.x < streams * streams && y1 != nullptr) s_mix[threadIdx.x] = mix[threadIdx.x];
+  if (threadIdx.x < streams) {
+    s_out[threadIdx.x] = y1 != nullptr ? out_w[threadIdx.x] : 0.f;
+    s_in[threadIdx.x] = in_w != nullptr ? in_w[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  const size_t r = blockIdx.x;
+  float* xr = xs + r * streams * cols;
+  float4 keep[SMV_KEEP];
+  float ssq = 0.f;
+#pragma unroll
+  for (int it = 0; it < SMV_KEEP; ++it) {
+    const int c = (threadIdx.x + it * ROW_THREADS) * 4;
+    keep[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c >= cols) continue;
+    float4 x[MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; ++s)
+      if (s < streams) x[s] = *reinterpret_cast<const float4*>(xr + static_cast<size_t>(s) * cols + c);
+    float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (y1 != nullptr) {
+      float4 y = load4<T>(y1 + r * cols + c);
+      y.x *= c1; y.y *= c1; y.z *= c1; y.w *= c1;
+      if (y2 != nullptr) {
+        const float4 z = load4<T>(y2 + r * cols + c);
+        y.x += c2 * z.x; y.y += c2 * z.y; y.z += c2 * z.z; y.w += c2 * z.w;
+      }
+#pragma unroll
+      for (int t = 0; t < MAX_STREAMS; ++t) {
+        if (t < streams) {
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int s = 0; s < MAX_STREAMS; ++s) {
+            if (s < streams) {
+              const float m = s_mix[s * streams + t];
+              acc.x += m * x[s].x; acc.y += m * x[s].y; acc.z += m * x[s].z; acc.w += m * x[s].w;
+            }
+          }
+          const float ow = s_out[t], iw = s_in[t];
+          acc.x += ow * y.x; acc.y += ow * y.y; acc.z += ow * y.z; acc.w += ow * y.w;
+          *reinterpret_cast<float4*>(xr + static_cast<size_t>(t) * cols + c) = acc;
+          u.x += iw * acc.x; u.y += iw * acc.y; u.z += iw * acc.z; u.w += iw * acc.w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < MAX_STREAMS; ++t) {
+        if (t < streams) {
+          const float iw = s_in[t];
+          u.x += iw * x[t].x; u.y += iw * x[t].y; u.z += iw * x[t].z; u.w += iw * x[t].w;
+        }
+      }
+    }
+    keep[it] = u;
+    ssq += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+  }
+  if (h == nullptr) return;
+  const float tot = block_sum(ssq, red);
+  const float inv = 1.0f / sqrtf(tot / static_cast<float>(cols) + eps);
+  T* hr = h + r * cols;
+#pragma unroll
+  for (int it = 0; it < SMV_KEEP; ++it) {
+    const int c = (threadIdx.x + it * ROW_THREADS) * 4;
+    if (c >= cols) continue;
+    const float4 w = *reinterpret_cast<const float4*>(norm_w + c);
+    const float4 u = keep[it];
+    store4<T>(hr + c, make_float4(u.x * inv * w.x, u.y * inv * w.y, u.z * inv * w.z, u.w * inv * w.w));
+  }
+}
+
 // out[i] = rms_norm(sum_s in_w[s] x_s of row rows_idx[i]) * norm_w
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
@@ -227,6 +322,77 @@ short_conv_act_kernel(const T* __restrict__ u, int64_t ldu, const float* __restr
   out[t * ldo + c] = from_f<T>(acc);
 }
 
+// The same convolution for TAPS known at compile time: a thread owns VEC = 16 / sizeof(T) consecutive channels and walks
+// CONV_RUN consecutive tokens of one sequence with its filters and the last TAPS - 1 rows in registers, so every row is
+// read once, as one 16-byte vector (channels, c_off and the row strides multiples of VEC; u, state, out 16-byte aligned).
+constexpr int CONV_RUN = 8;
+
+template <typename T> struct RowVec {
+  static constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+  static __device__ __forceinline__ void load(const T* p, float* f) {
+    const uint4 raw = ldg_v4(p);
+    if constexpr (VEC == 8) {
+      f[0] = bf16lo(raw.x); f[1] = bf16hi(raw.x); f[2] = bf16lo(raw.y); f[3] = bf16hi(raw.y);
+      f[4] = bf16lo(raw.z); f[5] = bf16hi(raw.z); f[6] = bf16lo(raw.w); f[7] = bf16hi(raw.w);
+    } else {
+      f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+    }
+  }
+  static __device__ __forceinline__ void store(T* p, const float* f) {
+    if constexpr (VEC == 8) stg_v4(p, make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7])));
+    else stg_v4(p, make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3])));
+  }
+};
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128)
+short_conv_act_run_kernel(const T* __restrict__ u, int64_t ldu, const float* __restrict__ w, const float* __restrict__ bias,
+                          const T* __restrict__ state, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
+                          const int32_t* __restrict__ seq_len, const int32_t* __restrict__ seq_slot, T* __restrict__ out,
+                          int64_t ldo, int C, int act) {
+  constexpr int VEC = RowVec<T>::VEC, R = TAPS - 1;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  const int b = blockIdx.z, t0 = blockIdx.x * CONV_RUN;
+  const int len = seq_len[b];
+  if (c >= C || t0 >= len) return;
+  const int pos0 = seq_pos0[b], start = seq_start[b];
+  const T* st = state + static_cast<size_t>(seq_slot[b]) * R * C;
+  float wt[TAPS][VEC], bs[VEC], win[TAPS][VEC];            // win[j]: the row TAPS - 1 - j tokens back
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    bs[e] = bias != nullptr ? bias[c + e] : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) wt[j][e] = w[(c + e) * TAPS + j];
+  }
+#pragma unroll
+  for (int j = 0; j < R; ++j) {                            // the rows before the run's first token
+    const int pj = pos0 + t0 - R + j;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) win[j][e] = 0.f;
+    if (pj >= pos0) RowVec<T>::load(u + static_cast<int64_t>(start + pj - pos0) * ldu + c, win[j]);
+    else if (pj >= 0) RowVec<T>::load(st + static_cast<size_t>(pj - (pos0 - R)) * C + c, win[j]);
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_RUN; ++i) {
+    const int t = t0 + i;
+    if (t >= len) break;
+    RowVec<T>::load(u + static_cast<int64_t>(start + t) * ldu + c, win[R]);
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      float a = bs[e];
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) a += wt[j][e] * win[j][e];
+      acc[e] = act == 1 ? silu_f(a) : a;
+    }
+    RowVec<T>::store(out + static_cast<int64_t>(start + t) * ldo + c, acc);
+#pragma unroll
+    for (int j = 0; j < R; ++j)
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) win[j][e] = win[j + 1][e];
+  }
+}
+
 // The carried state after the step: entry r holds the row of position end - R + r (end = pos0 + new tokens).  One thread
 // per (sequence, column) reads its old entries before it writes any, so the shift is safe in place.
 template <typename T>
@@ -294,6 +460,45 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate,
   }
 }
 
+// The same for groups of a size that is a multiple of four (y 16-byte aligned rows, gate and out 8- / 16-byte aligned).
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+gated_group_norm_vec4_kernel(const float* __restrict__ y, const T* __restrict__ gate, int64_t ldg, const float* __restrict__ w,
+                             int w_len, int groups, int act, int gate_first, float eps, T* __restrict__ out, int cols) {
+  __shared__ float red[33];
+  const size_t r = blockIdx.x;
+  const int gs = cols / groups, c0 = blockIdx.y * gs;
+  const float* yr = y + r * cols + c0;
+  const T* gr = gate != nullptr ? gate + r * ldg + c0 : nullptr;
+  auto gated = [&](int c, float4& v, float4& g) {
+    v = *reinterpret_cast<const float4*>(yr + c);
+    g = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (gr != nullptr) {
+      const float4 z = load4<T>(gr + c);
+      if (act == 0) g = make_float4(sigmoid_f(z.x), sigmoid_f(z.y), sigmoid_f(z.z), sigmoid_f(z.w));
+      else g = make_float4(silu_f(z.x), silu_f(z.y), silu_f(z.z), silu_f(z.w));
+    }
+    if (gate_first) { v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w; }
+  };
+  float ssq = 0.f;
+  for (int c = threadIdx.x * 4; c < gs; c += blockDim.x * 4) {
+    float4 v, g;
+    gated(c, v, g);
+    ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ssq, red) / static_cast<float>(gs) + eps);
+  T* o = out + r * cols + c0;
+  for (int c = threadIdx.x * 4; c < gs; c += blockDim.x * 4) {
+    float4 v, g;
+    gated(c, v, g);
+    const int wc = (c0 + c) % w_len;                       // w_len is a multiple of four here
+    const float4 ww = *reinterpret_cast<const float4*>(w + wc);
+    float4 res = make_float4(v.x * inv * ww.x, v.y * inv * ww.y, v.z * inv * ww.z, v.w * inv * ww.w);
+    if (!gate_first) { res.x *= g.x; res.y *= g.y; res.z *= g.z; res.w *= g.w; }
+    store4<T>(o + c, res);
+  }
+}
+
 }  // namespace row
 }  // namespace b2
 
@@ -330,7 +535,15 @@ extern "C" int b2tts_stream_mix_norm(float* xs, const void* y1, const void* y2, 
   if (rows == 0) return B2TTS_OK;
   B2_REQUIRE(xs && (!y1 || (mix && out_w)) && (y1 || !y2) && (!h || norm_w), B2TTS_EINVAL, "stream_mix_norm: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == B2TTS_DTYPE_BF16)
+  const bool vec4 = cols % 4 == 0 && cols <= 4 * SMV_KEEP * ROW_THREADS && aligned16(xs) && aligned16(norm_w) &&
+                    (!y1 || aligned16(y1)) && (!y2 || aligned16(y2)) && (!h || aligned16(h));
+  if (vec4 && dtype == B2TTS_DTYPE_BF16)
+    stream_mix_norm_vec4_kernel<__nv_bfloat16><<<rows, ROW_THREADS, 0, st>>>(xs, static_cast<const __nv_bfloat16*>(y1),
+        static_cast<const __nv_bfloat16*>(y2), c1, c2, mix, out_w, in_w, norm_w, static_cast<__nv_bfloat16*>(h), cols, streams, eps);
+  else if (vec4)
+    stream_mix_norm_vec4_kernel<float><<<rows, ROW_THREADS, 0, st>>>(xs, static_cast<const float*>(y1), static_cast<const float*>(y2),
+        c1, c2, mix, out_w, in_w, norm_w, static_cast<float*>(h), cols, streams, eps);
+  else if (dtype == B2TTS_DTYPE_BF16)
     stream_mix_norm_kernel<__nv_bfloat16><<<rows, ROW_THREADS, 0, st>>>(xs, static_cast<const __nv_bfloat16*>(y1),
         static_cast<const __nv_bfloat16*>(y2), c1, c2, mix, out_w, in_w, norm_w, static_cast<__nv_bfloat16*>(h), cols, streams, eps);
   else
@@ -386,11 +599,25 @@ template <typename T>
 static void launch_conv_act(cudaStream_t st, const void* u, int64_t ldu, int c_off, const float* w, const float* bias, void* state,
                             const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_start, const int32_t* seq_pos0,
                             const int32_t* seq_len, const int32_t* seq_slot, void* out, int64_t ldo, int n_tokens, int n_seqs,
-                            int C, int taps, int act) {
+                            int max_new, int C, int taps, int act) {
   const T* uu = static_cast<const T*>(u) + c_off;
-  short_conv_act_kernel<T><<<dim3(n_tokens, (C + ROW_THREADS - 1) / ROW_THREADS), ROW_THREADS, 0, st>>>(
-      uu, ldu, w, bias, static_cast<const T*>(state), tok_seq, positions, seq_start, seq_pos0, seq_len, seq_slot,
-      static_cast<T*>(out), ldo, C, taps, act);
+  constexpr int VEC = 16 / static_cast<int>(sizeof(T));
+  const bool vec = taps >= 2 && taps <= 4 && max_new > 0 && C % VEC == 0 && ldu % VEC == 0 && ldo % VEC == 0 && aligned16(uu) &&
+                   aligned16(out) && aligned16(state) && n_seqs <= 65535;
+  if (vec) {
+    const int threads = std::min(128, (C / VEC + 31) / 32 * 32);
+    const dim3 grid((max_new + CONV_RUN - 1) / CONV_RUN, (C / VEC + threads - 1) / threads, n_seqs);
+#define CONV_RUN_GO(TP) short_conv_act_run_kernel<T, TP><<<grid, threads, 0, st>>>(uu, ldu, w, bias, static_cast<const T*>(state), seq_start, \
+        seq_pos0, seq_len, seq_slot, static_cast<T*>(out), ldo, C, act)
+    if (taps == 4) CONV_RUN_GO(4);
+    else if (taps == 3) CONV_RUN_GO(3);
+    else CONV_RUN_GO(2);
+#undef CONV_RUN_GO
+  } else {
+    short_conv_act_kernel<T><<<dim3(n_tokens, (C + ROW_THREADS - 1) / ROW_THREADS), ROW_THREADS, 0, st>>>(
+        uu, ldu, w, bias, static_cast<const T*>(state), tok_seq, positions, seq_start, seq_pos0, seq_len, seq_slot,
+        static_cast<T*>(out), ldo, C, taps, act);
+  }
   if (taps > 1)
     conv_state_advance_kernel<T><<<dim3((C + 127) / 128, n_seqs), 128, 0, st>>>(uu, ldu, static_cast<T*>(state), seq_start, seq_pos0,
                                                                                seq_len, seq_slot, C, taps);
@@ -399,8 +626,8 @@ static void launch_conv_act(cudaStream_t st, const void* u, int64_t ldu, int c_o
 extern "C" int b2tts_short_conv_act(const void* u, int64_t ldu, int c_off, const float* w, const float* bias, void* state,
                                     const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_start,
                                     const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot, void* out,
-                                    int64_t ldo, int n_tokens, int n_seqs, int channels, int taps, int act, int dtype,
-                                    void* stream) {
+                                    int64_t ldo, int n_tokens, int n_seqs, int max_new, int channels, int taps, int act,
+                                    int dtype, void* stream) {
   B2_REQUIRE(n_tokens >= 0 && n_seqs >= 0 && channels > 0 && c_off >= 0, B2TTS_EINVAL, "short_conv_act: bad sizes");
   B2_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, B2TTS_EUNSUPPORTED, "short_conv_act: taps %d not in 1..%d", taps, CONV_MAX_TAPS);
   B2_REQUIRE(act == 0 || act == 1, B2TTS_EINVAL, "short_conv_act: act %d", act);
@@ -411,10 +638,10 @@ extern "C" int b2tts_short_conv_act(const void* u, int64_t ldu, int c_off, const
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == B2TTS_DTYPE_BF16)
     launch_conv_act<__nv_bfloat16>(st, u, ldu, c_off, w, bias, state, tok_seq, positions, seq_start, seq_pos0, seq_len, seq_slot, out,
-                                   ldo, n_tokens, n_seqs, channels, taps, act);
+                                   ldo, n_tokens, n_seqs, max_new, channels, taps, act);
   else
     launch_conv_act<float>(st, u, ldu, c_off, w, bias, state, tok_seq, positions, seq_start, seq_pos0, seq_len, seq_slot, out, ldo,
-                           n_tokens, n_seqs, channels, taps, act);
+                           n_tokens, n_seqs, max_new, channels, taps, act);
   B2_CHECK_LAUNCH("short_conv_act");
   return B2TTS_OK;
 }
@@ -430,8 +657,21 @@ extern "C" int b2tts_gated_group_norm(const float* y, const void* gate, int64_t 
   B2_REQUIRE(y && w && out, B2TTS_EINVAL, "gated_group_norm: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int gs = cols / groups;
-  const int threads = std::min(ROW_THREADS, (gs + 31) / 32 * 32);
   const dim3 grid(rows, groups);
+  const bool vec4 = gs % 4 == 0 && w_len % 4 == 0 && ldg % 4 == 0 && aligned16(y) && aligned16(w) && aligned16(out) &&
+                    (!gate || aligned16(gate));
+  if (vec4) {
+    const int threads = std::min(ROW_THREADS, (gs / 4 + 31) / 32 * 32);
+    if (dtype == B2TTS_DTYPE_BF16)
+      gated_group_norm_vec4_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(y, static_cast<const __nv_bfloat16*>(gate), ldg, w, w_len,
+          groups, gate_act, gate_first, eps, static_cast<__nv_bfloat16*>(out), cols);
+    else
+      gated_group_norm_vec4_kernel<float><<<grid, threads, 0, st>>>(y, static_cast<const float*>(gate), ldg, w, w_len, groups, gate_act,
+                                                                   gate_first, eps, static_cast<float*>(out), cols);
+    B2_CHECK_LAUNCH("gated_group_norm");
+    return B2TTS_OK;
+  }
+  const int threads = std::min(ROW_THREADS, (gs + 31) / 32 * 32);
   if (dtype == B2TTS_DTYPE_BF16)
     gated_group_norm_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(y, static_cast<const __nv_bfloat16*>(gate), ldg, w, w_len, groups,
                                                                     gate_act, gate_first, eps, static_cast<__nv_bfloat16*>(out), cols);

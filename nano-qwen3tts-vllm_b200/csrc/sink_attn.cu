@@ -7,10 +7,11 @@
 // Both masks are a lower bound on j, so one kernel serves them.  The sink has no key and no value and is not scaled.  An
 // optional per-head gate multiplies the head's output by sigmoid(gate[t, h]).
 //
-// Plain kernel (bf16 or float, any head size up to 256): one CTA of four warps per (token, query head).  A warp takes
-// 32-key tiles: each lane scores one key against the query held in shared memory (float accumulation), the warp keeps a
-// running maximum and denominator, and the lanes then split the value columns for the weighted sum.  The four warps'
-// partial results are merged through shared memory.  Scores, weights and sums are float in both modes.
+// Plain kernel (bf16 or float, any head size up to 256): one CTA of four warps per token and 1, 2 or 4 query heads of one
+// key/value group, so a cached row is loaded once for all of them.  A warp takes 32-key tiles: each lane scores one key
+// against the queries held in shared memory (float accumulation), the warp keeps a running maximum and denominator per
+// head, and the lanes then split the value columns for the weighted sums.  The four warps' partial results are merged
+// through shared memory.  Scores, weights and sums are float in both modes.
 #include <math.h>
 
 #include "row_ops.cuh"
@@ -20,31 +21,11 @@ namespace row {
 
 constexpr int SA_WARPS = 4;
 constexpr int SA_MAX_PER_LANE = 8;        // value sizes up to 256
+constexpr int SA_ROWS_AHEAD = 8;          // value rows in flight per lane
 
 template <typename T> struct Vec16;       // how many T fit 16 bytes
 template <> struct Vec16<float> { static constexpr int N = 4; };
 template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
-
-template <typename T>
-__device__ __forceinline__ float dot_row(const T* __restrict__ kr, const float* __restrict__ q, int d, bool vec) {
-  float acc = 0.f;
-  if (vec) {
-    constexpr int N = Vec16<T>::N;
-    for (int c = 0; c < d; c += N) {
-      const uint4 raw = ldg_v4(kr + c);
-      if constexpr (N == 8) {
-        acc += bf16lo(raw.x) * q[c] + bf16hi(raw.x) * q[c + 1] + bf16lo(raw.y) * q[c + 2] + bf16hi(raw.y) * q[c + 3] +
-               bf16lo(raw.z) * q[c + 4] + bf16hi(raw.z) * q[c + 5] + bf16lo(raw.w) * q[c + 6] + bf16hi(raw.w) * q[c + 7];
-      } else {
-        acc += __uint_as_float(raw.x) * q[c] + __uint_as_float(raw.y) * q[c + 1] + __uint_as_float(raw.z) * q[c + 2] +
-               __uint_as_float(raw.w) * q[c + 3];
-      }
-    }
-  } else {
-    for (int c = 0; c < d; ++c) acc += to_f(kr[c]) * q[c];
-  }
-  return acc;
-}
 
 // `cpl` consecutive value columns of one cached row -> floats; `bytes` = cpl * sizeof(T) when the row allows vector loads, else 0
 template <typename T>
@@ -71,7 +52,51 @@ __device__ __forceinline__ void load_cols(const T* __restrict__ p, int cpl, int 
   }
 }
 
-template <typename T>
+// REP query heads of one key/value group share the CTA: a key row and a value row are loaded once and serve all of them.
+template <typename T, int REP>
+__device__ __forceinline__ void dot_rows(const T* __restrict__ kr, const float* __restrict__ q, int d, int qs_stride, bool vec, float* s) {
+#pragma unroll
+  for (int r = 0; r < REP; ++r) s[r] = 0.f;
+  if (vec) {
+    constexpr int N = Vec16<T>::N, B = 8;              // eight 16-byte pieces of the row are asked for before the first is used
+    for (int c0 = 0; c0 < d; c0 += B * N) {
+      uint4 raw[B];
+#pragma unroll
+      for (int i = 0; i < B; ++i) raw[i] = c0 + i * N < d ? ldg_v4(kr + c0 + i * N) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < B; ++i) {
+        const int c = c0 + i * N;
+        if (c < d) {
+          float f[8];
+          if constexpr (N == 8) {
+            f[0] = bf16lo(raw[i].x); f[1] = bf16hi(raw[i].x); f[2] = bf16lo(raw[i].y); f[3] = bf16hi(raw[i].y);
+            f[4] = bf16lo(raw[i].z); f[5] = bf16hi(raw[i].z); f[6] = bf16lo(raw[i].w); f[7] = bf16hi(raw[i].w);
+          } else {
+            f[0] = __uint_as_float(raw[i].x); f[1] = __uint_as_float(raw[i].y); f[2] = __uint_as_float(raw[i].z); f[3] = __uint_as_float(raw[i].w);
+          }
+#pragma unroll
+          for (int r = 0; r < REP; ++r) {
+            const float4* qr = reinterpret_cast<const float4*>(q + r * qs_stride + c);
+            const float4 qa = qr[0];
+            s[r] += f[0] * qa.x + f[1] * qa.y + f[2] * qa.z + f[3] * qa.w;
+            if constexpr (N == 8) {
+              const float4 qb = qr[1];
+              s[r] += f[4] * qb.x + f[5] * qb.y + f[6] * qb.z + f[7] * qb.w;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    for (int c = 0; c < d; ++c) {
+      const float kv = to_f(kr[c]);
+#pragma unroll
+      for (int r = 0; r < REP; ++r) s[r] += kv * q[r * qs_stride + c];
+    }
+  }
+}
+
+template <typename T, int REP>
 __global__ void __launch_bounds__(SA_WARPS * 32)
 sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_len,
@@ -79,23 +104,24 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  const T* __restrict__ gate, int64_t ldg, int H, int G, int d, int dv, int page, int mask_kind, int mask,
                  float scale, int only_single) {
   extern __shared__ float smem[];
-  float* qs = smem;                                   // [d]
-  float* part = smem + ((d + 3) & ~3);                // [SA_WARPS][dv + 2]: sums, running maximum, denominator
+  const int qstride = (d + 3) & ~3;
+  float* qs = smem;                                   // [REP][qstride]
+  float* part = smem + REP * qstride;                 // [SA_WARPS][REP][dv + 2]: sums, running maximum, denominator
   const size_t t = blockIdx.x;
-  const int h = blockIdx.y, g = h / (H / G);
+  const int h0 = blockIdx.y * REP, g = h0 / (H / G);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int b = tok_seq[t];
-  T* orow = out + (t * H + h) * dv;
+  T* orow = out + (t * H + h0) * dv;                  // the REP heads' outputs are adjacent
   if (only_single && seq_len[b] > 1) return;          // the tensor-core kernel owns prompt portions
   if (seq_len[b] <= 0) {                              // padding row
-    for (int c = threadIdx.x; c < dv; c += blockDim.x) orow[c] = from_f<T>(0.f);
+    for (int c = threadIdx.x; c < REP * dv; c += blockDim.x) orow[c] = from_f<T>(0.f);
     return;
   }
   const int i = positions[t];
   int lo = 0;
   if (mask > 0) lo = mask_kind == 0 ? max(0, i - mask + 1) : (i / mask) * mask;
-  const T* qr = q + (t * H + h) * d;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) qs[c] = to_f(qr[c]);
+  const T* qr = q + (t * H + h0) * d;
+  for (int c = threadIdx.x; c < REP * d; c += blockDim.x) qs[(c / d) * qstride + c % d] = to_f(qr[c]);
   __syncthreads();
   const int32_t* bt = block_tables + static_cast<int64_t>(b) * bt_stride;
   const int nk = G * d, nv = G * dv;
@@ -105,65 +131,121 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
   const int cbytes = cpl * static_cast<int>(sizeof(T));
   const int vbytes = (dv % 32 == 0 && (cbytes == 4 || cbytes == 8 || cbytes == 16 || cbytes == 32)) ? cbytes : 0;
   const int room = max(0, min(cpl, dv - c_lane));
-  float m = -INFINITY, l = 0.f;
-  float acc[SA_MAX_PER_LANE];
+  float m[REP], l[REP], acc[REP][SA_MAX_PER_LANE];
 #pragma unroll
-  for (int x = 0; x < SA_MAX_PER_LANE; ++x) acc[x] = 0.f;
+  for (int r = 0; r < REP; ++r) {
+    m[r] = -INFINITY; l[r] = 0.f;
+#pragma unroll
+    for (int x = 0; x < SA_MAX_PER_LANE; ++x) acc[r][x] = 0.f;
+  }
   const int n_keys = i - lo + 1;
   for (int j0 = warp * 32; j0 < n_keys; j0 += SA_WARPS * 32) {
     const int j = lo + j0 + lane;
-    float s = -INFINITY;
+    float sc[REP], p[REP];
     int slot = 0;
+#pragma unroll
+    for (int r = 0; r < REP; ++r) sc[r] = -INFINITY;
     if (j <= i) {
       slot = bt[j / page] * page + j % page;
-      s = dot_row<T>(k_cache + static_cast<size_t>(slot) * nk + g * d, qs, d, vec) * scale;
+      dot_rows<T, REP>(k_cache + static_cast<size_t>(slot) * nk + g * d, qs, d, qstride, vec, sc);
     }
-    const float m_new = fmaxf(m, warp_max(s));        // finite: the tile's first key exists
-    const float p = j <= i ? expf(s - m_new) : 0.f;
-    const float corr = expf(m - m_new);               // 0 on the first tile (m = -inf)
-    l = l * corr + warp_sum(p);
-    m = m_new;
 #pragma unroll
-    for (int x = 0; x < SA_MAX_PER_LANE; ++x) acc[x] *= corr;
+    for (int r = 0; r < REP; ++r) {
+      const float s = j <= i ? sc[r] * scale : -INFINITY;
+      const float m_new = fmaxf(m[r], warp_max(s));   // finite: the tile's first key exists
+      p[r] = j <= i ? expf(s - m_new) : 0.f;
+      const float corr = expf(m[r] - m_new);          // 0 on the first tile (m = -inf)
+      l[r] = l[r] * corr + warp_sum(p[r]);
+      m[r] = m_new;
+#pragma unroll
+      for (int x = 0; x < SA_MAX_PER_LANE; ++x) acc[r][x] *= corr;
+    }
+    // four value rows are asked for before the first is used: their loads overlap
     const int cnt = min(32, n_keys - j0);
-    for (int kk = 0; kk < cnt; ++kk) {
-      const float pk = __shfl_sync(0xffffffffu, p, kk);
-      const int sk = __shfl_sync(0xffffffffu, slot, kk);
-      float vf[SA_MAX_PER_LANE];
-      load_cols<T>(v_cache + static_cast<size_t>(sk) * nv + g * dv + (room > 0 ? c_lane : 0), cpl, vbytes, room, vf);
+    for (int kk0 = 0; kk0 < cnt; kk0 += SA_ROWS_AHEAD) {
+      float vf[SA_ROWS_AHEAD][SA_MAX_PER_LANE];
 #pragma unroll
-      for (int x = 0; x < SA_MAX_PER_LANE; ++x) acc[x] += pk * vf[x];
+      for (int u = 0; u < SA_ROWS_AHEAD; ++u) {
+        const int sk = __shfl_sync(0xffffffffu, slot, (kk0 + u) & 31);
+        if (kk0 + u < cnt) {
+          load_cols<T>(v_cache + static_cast<size_t>(sk) * nv + g * dv + (room > 0 ? c_lane : 0), cpl, vbytes, room, vf[u]);
+        } else {
+#pragma unroll
+          for (int x = 0; x < SA_MAX_PER_LANE; ++x) vf[u][x] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < SA_ROWS_AHEAD; ++u) {
+#pragma unroll
+        for (int r = 0; r < REP; ++r) {
+          float pk = __shfl_sync(0xffffffffu, p[r], (kk0 + u) & 31);
+          if (kk0 + u >= cnt) pk = 0.f;
+#pragma unroll
+          for (int x = 0; x < SA_MAX_PER_LANE; ++x) acc[r][x] += pk * vf[u][x];
+        }
+      }
     }
   }
-  float* mine = part + warp * (dv + 2);
+  const int pstride = dv + 2;
 #pragma unroll
-  for (int x = 0; x < SA_MAX_PER_LANE; ++x)
-    if (x < room) mine[c_lane + x] = acc[x];
-  if (lane == 0) { mine[dv] = m; mine[dv + 1] = l; }
-  __syncthreads();
-  const float sk = sink != nullptr ? sink[h] : -INFINITY;
-  float mm = sk;
+  for (int r = 0; r < REP; ++r) {
+    float* mine = part + (warp * REP + r) * pstride;
 #pragma unroll
-  for (int w = 0; w < SA_WARPS; ++w) mm = fmaxf(mm, part[w * (dv + 2) + dv]);
-  float den = sink != nullptr ? expf(sk - mm) : 0.f;
-  float cw[SA_WARPS];
-#pragma unroll
-  for (int w = 0; w < SA_WARPS; ++w) {
-    const float mw = part[w * (dv + 2) + dv];
-    cw[w] = mw == -INFINITY ? 0.f : expf(mw - mm);
-    den += cw[w] * part[w * (dv + 2) + dv + 1];
+    for (int x = 0; x < SA_MAX_PER_LANE; ++x)
+      if (x < room) mine[c_lane + x] = acc[r][x];
+    if (lane == 0) { mine[dv] = m[r]; mine[dv + 1] = l[r]; }
   }
-  float gv = 1.f;
-  if (gate != nullptr) gv = sigmoid_f(to_f(gate[t * ldg + h]));
-  const float inv = gv / den;
-  for (int c = threadIdx.x; c < dv; c += blockDim.x) {
-    float o = 0.f;
+  __syncthreads();
 #pragma unroll
-    for (int w = 0; w < SA_WARPS; ++w) o += cw[w] * part[w * (dv + 2) + c];
-    orow[c] = from_f<T>(o * inv);
+  for (int r = 0; r < REP; ++r) {
+    const int h = h0 + r;
+    const float sk = sink != nullptr ? sink[h] : -INFINITY;
+    float mm = sk;
+#pragma unroll
+    for (int w = 0; w < SA_WARPS; ++w) mm = fmaxf(mm, part[(w * REP + r) * pstride + dv]);
+    float den = sink != nullptr ? expf(sk - mm) : 0.f;
+    float cw[SA_WARPS];
+#pragma unroll
+    for (int w = 0; w < SA_WARPS; ++w) {
+      const float mw = part[(w * REP + r) * pstride + dv];
+      cw[w] = mw == -INFINITY ? 0.f : expf(mw - mm);
+      den += cw[w] * part[(w * REP + r) * pstride + dv + 1];
+    }
+    float gv = 1.f;
+    if (gate != nullptr) gv = sigmoid_f(to_f(gate[t * ldg + h]));
+    const float inv = gv / den;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < SA_WARPS; ++w) o += cw[w] * part[(w * REP + r) * pstride + c];
+      orow[r * dv + c] = from_f<T>(o * inv);
+    }
   }
 }
 
+template <typename T, int REP>
+static void launch_sink_plain(cudaStream_t st, const void* q, const void* kc, const void* vc, void* out, const int32_t* tok_seq,
+                              const int32_t* positions, const int32_t* seq_len, const int32_t* bt, int64_t bt_stride, const float* sink,
+                              const void* gate, int64_t ldg, int n_tokens, int H, int G, int d, int dv, int page, int mask_kind, int mask,
+                              float scale, int only_single) {
+  const size_t sm = (static_cast<size_t>(REP) * ((d + 3) & ~3) + static_cast<size_t>(SA_WARPS) * REP * (dv + 2)) * sizeof(float);
+  sink_attn_kernel<T, REP><<<dim3(n_tokens, H / REP), SA_WARPS * 32, sm, st>>>(
+      static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), tok_seq, positions, seq_len, bt,
+      bt_stride, sink, static_cast<const T*>(gate), ldg, H, G, d, dv, page, mask_kind, mask, scale, only_single);
+}
+
+template <typename T>
+static void launch_sink_plain_rep(int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
+                                  const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_len, const int32_t* bt,
+                                  int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_tokens, int H, int G, int d,
+                                  int dv, int page, int mask_kind, int mask, float scale, int only_single) {
+#define SINK_PLAIN_ARGS st, q, kc, vc, out, tok_seq, positions, seq_len, bt, bt_stride, sink, gate, ldg, n_tokens, H, G, d, dv, page, mask_kind, mask, scale, only_single
+  // heads of a group that share a CTA: as many as divide the group, up to four (two for wide values: registers)
+  if (rep % 4 == 0 && dv <= 128) launch_sink_plain<T, 4>(SINK_PLAIN_ARGS);
+  else if (rep % 2 == 0) launch_sink_plain<T, 2>(SINK_PLAIN_ARGS);
+  else launch_sink_plain<T, 1>(SINK_PLAIN_ARGS);
+#undef SINK_PLAIN_ARGS
+}
 
 // ------------------------------------------------------------------ prompt portions on the tensor cores (bf16)
 // 64 query tokens of one head per CTA (4 warps x 16 rows); key tiles of 64 are gathered through the block table into
@@ -434,17 +516,13 @@ extern "C" int b2tts_sink_attn(const void* q, const void* k_cache, const void* v
     if (e != cudaSuccess) return cuda_fail(e, "sink_attn (tensor cores)");
     B2_CHECK_LAUNCH("sink_attn (tensor cores)");
   }
-  const size_t sm = (((dim + 3) & ~3) + SA_WARPS * (vdim + 2)) * sizeof(float);
-  const dim3 grid(n_tokens, heads);
   if (dtype == B2TTS_DTYPE_BF16)
-    sink_attn_kernel<__nv_bfloat16><<<grid, SA_WARPS * 32, sm, st>>>(static_cast<const __nv_bfloat16*>(q),
-        static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache), static_cast<__nv_bfloat16*>(out), tok_seq,
-        positions, seq_len, block_tables, bt_stride, sink, static_cast<const __nv_bfloat16*>(gate), ldg, heads, kv_heads, dim, vdim, page,
-        mask_kind, mask, scale, use_mma ? 1 : 0);
+    launch_sink_plain_rep<__nv_bfloat16>(heads / kv_heads, st, q, k_cache, v_cache, out, tok_seq, positions, seq_len, block_tables,
+                                         bt_stride, sink, gate, ldg, n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale,
+                                         use_mma ? 1 : 0);
   else
-    sink_attn_kernel<float><<<grid, SA_WARPS * 32, sm, st>>>(static_cast<const float*>(q), static_cast<const float*>(k_cache),
-        static_cast<const float*>(v_cache), static_cast<float*>(out), tok_seq, positions, seq_len, block_tables, bt_stride, sink,
-        static_cast<const float*>(gate), ldg, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, 0);
+    launch_sink_plain_rep<float>(heads / kv_heads, st, q, k_cache, v_cache, out, tok_seq, positions, seq_len, block_tables, bt_stride,
+                                 sink, gate, ldg, n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, 0);
   B2_CHECK_LAUNCH("sink_attn");
   return B2TTS_OK;
 }
