@@ -591,8 +591,8 @@ B2TTS_API int b2tts_delta_rule_scan(const void* qkv, int64_t ldq, const void* be
 B2TTS_API int b2tts_matrix_memory_scan(const void* q, const void* k, const void* v, const void* ig, const void* fg, int64_t ldu,
                                        const float* i_bias, const float* f_bias, float cap, float* state, float* state_nm,
                                        float* gates, float* out, const int32_t* seq_start, const int32_t* seq_pos0,
-                                       const int32_t* seq_len, const int32_t* seq_slot, int n_seqs, int heads, int dim, int vdim,
-                                       int dtype, void* stream);
+                                       const int32_t* seq_len, const int32_t* seq_slot, int n_tokens, int n_seqs, int heads, int dim,
+                                       int vdim, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -107,7 +107,7 @@ def _load():
         "b2tts_gated_group_norm": (I, [P, P, L, P, I, I, I, I, F, P, I, I, I, P]),
         "b2tts_ssm_scan": (I, [P, L, P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
         "b2tts_delta_rule_scan": (I, [P, L, P, P, L, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
-        "b2tts_matrix_memory_scan": (I, [P, P, P, P, P, L, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, P]),
+        "b2tts_matrix_memory_scan": (I, [P, P, P, P, P, L, P, P, F, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
         "b2tts_grouped_gemm": (I, [P, L, P, P, L, P, P, I, I, I, I, I, I, I, I, I, P]),
     }
     for name, (res, args) in sig.items():
@@ -1037,5 +1037,5 @@ def matrix_memory_scan(q, k, v, ig, fg, i_bias, f_bias, cap, state, state_nm, ga
         _cuda(t, F32, "state"); assert t.is_contiguous()
     _check(_load().b2tts_matrix_memory_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), ig.data_ptr(), fg.data_ptr(), q.stride(0),
                                             i_bias.data_ptr(), f_bias.data_ptr(), cap, state.data_ptr(), state_nm.data_ptr(),
-                                            gates.data_ptr(), out.data_ptr(), *_seq_args(lay), heads, dim, vdim, dt, _stream()),
+                                            gates.data_ptr(), out.data_ptr(), *_seq_args(lay, True), heads, dim, vdim, dt, _stream()),
            "matrix_memory_scan")

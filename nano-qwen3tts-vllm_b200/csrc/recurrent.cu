@@ -176,15 +176,19 @@ scan_kernel(const ScanArgs a) {
 // ------------------------------------------------------------------ per-token scalars of the state space and the delta rule
 // kind 0: dt = softplus(s1 + f1[h]); coef = (exp(-exp(f2[h]) dt), dt, 1)                       (f1 = dt_bias, f2 = A_log)
 // kind 1: coef = (exp(-exp(f1[h]) softplus(s2 + f2[h])), sigmoid(s1), 1)                      (f1 = A_log, f2 = dt_bias)
+// kind 2: coef = (log input gate, log forget gate, 1) of the matrix memory                   (f1, f2 = the gates' biases)
 template <typename T>
 __global__ void scan_coef_kernel(const T* __restrict__ s1, const T* __restrict__ s2, int64_t lds, const float* __restrict__ f1,
-                                 const float* __restrict__ f2, float* __restrict__ coef, int n_tokens, int H, int kind) {
+                                 const float* __restrict__ f2, float* __restrict__ coef, int n_tokens, int H, int kind, float cap) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_tokens * H) return;
   const size_t t = idx / H;
   const int h = idx % H;
   float c0, c1;
-  if (kind == 0) {
+  if (kind == 2) {                                       // log gates: cap tanh((s1 + f1) / cap), logsigmoid(cap tanh((s2 + f2) / cap))
+    c0 = cap * tanhf((to_f(s1[t * lds + h]) + f1[h]) / cap);
+    c1 = logsigmoid_f(cap * tanhf((to_f(s2[t * lds + h]) + f2[h]) / cap));
+  } else if (kind == 0) {
     const float dt = softplus_f(to_f(s1[t * lds + h]) + f1[h]);
     c0 = expf(-expf(f2[h]) * dt);
     c1 = dt;
@@ -197,15 +201,14 @@ __global__ void scan_coef_kernel(const T* __restrict__ s1, const T* __restrict__
 }
 
 // ------------------------------------------------------------------ scalar part of the matrix memory
-// One warp per (sequence, head).  i = cap tanh((ig + bi) / cap), f = logsigmoid(cap tanh((fg + bf) / cap));
+// One warp per (sequence, head).  The log gates i = cap tanh((ig + bi) / cap), f = logsigmoid(cap tanh((fg + bf) / cap)) of
+// all tokens come from the kernel in front (they do not depend on the state); here, token by token:
 // m' = max(f + m, i), a = exp(f + m - m'), b = exp(i - m'); n <- a n + b k; den = max(|n . q * qscale|, exp(-m')) + 1e-6.
 // state_nm [slots, H, d + 1]: n, then m (m starts at 0).  The next token's inputs are fetched while this one is computed.
 template <typename T>
 __global__ void __launch_bounds__(32)
-matrix_memory_gates_kernel(const T* __restrict__ k, const T* __restrict__ q, const T* __restrict__ ig, const T* __restrict__ fg,
-                           int64_t ldu, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
-                           float qscale, float* __restrict__ state_nm, float* __restrict__ gates,
-                           const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
+matrix_memory_gates_kernel(const T* __restrict__ k, const T* __restrict__ q, int64_t ldu, float qscale, float* __restrict__ state_nm,
+                           float* __restrict__ gates, const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                            const int32_t* __restrict__ seq_len, const int32_t* __restrict__ seq_slot, int H, int d) {
   const int b = blockIdx.y, h = blockIdx.x;
   const int len = seq_len[b];
@@ -213,14 +216,14 @@ matrix_memory_gates_kernel(const T* __restrict__ k, const T* __restrict__ q, con
   const int start = seq_start[b], pos0 = seq_pos0[b], lane = threadIdx.x;
   float* nm = state_nm + (static_cast<size_t>(seq_slot[b]) * H + h) * (d + 1);
   float n[SCAN_PER];
-  T rk[SCAN_PER], rq[SCAN_PER], ri, rf;                    // the next token's inputs, converted only when they are used
+  T rk[SCAN_PER], rq[SCAN_PER];                            // the next token's inputs, converted only when they are used
+  float ri = 0.f, rf = 0.f;
 #pragma unroll
   for (int x = 0; x < SCAN_PER; ++x) {
     const int i = lane + x * 32;
     n[x] = (i < d && pos0 > 0) ? nm[i] : 0.f;
   }
   float m = pos0 > 0 ? nm[d] : 0.f;
-  const float bi = i_bias[h], bf = f_bias[h];
   auto fetch = [&](int t) {
     const size_t r = static_cast<size_t>(start + t);
 #pragma unroll
@@ -229,13 +232,13 @@ matrix_memory_gates_kernel(const T* __restrict__ k, const T* __restrict__ q, con
       rk[x] = rq[x] = from_f<T>(0.f);
       if (i < d) { rk[x] = k[r * ldu + h * d + i]; rq[x] = q[r * ldu + h * d + i]; }
     }
-    ri = ig[r * ldu + h];
-    rf = fg[r * ldu + h];
+    const float* gp = gates + (r * H + h) * 3;             // the log gates, left there by the kernel in front
+    ri = gp[0];
+    rf = gp[1];
   };
   fetch(0);
   for (int t = 0; t < len; ++t) {
-    const float li = cap * tanhf((to_f(ri) + bi) / cap);
-    const float lf = logsigmoid_f(cap * tanhf((to_f(rf) + bf) / cap));
+    const float li = ri, lf = rf;
     const float m_new = fmaxf(lf + m, li);
     const float ca = expf(lf + m - m_new), cb = expf(li - m_new);
     m = m_new;
@@ -278,10 +281,10 @@ static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t st, const cha
 
 template <typename T>
 static void launch_coef(const void* s1, const void* s2, int64_t lds, const float* f1, const float* f2, float* coef, int n_tokens, int H,
-                        int kind, cudaStream_t st) {
+                        int kind, cudaStream_t st, float cap = 1.f) {
   const int total = n_tokens * H;
   scan_coef_kernel<T><<<(total + 255) / 256, 256, 0, st>>>(static_cast<const T*>(s1), static_cast<const T*>(s2), lds, f1, f2, coef,
-                                                          n_tokens, H, kind);
+                                                          n_tokens, H, kind, cap);
 }
 
 }  // namespace row
@@ -361,9 +364,10 @@ extern "C" int b2tts_delta_rule_scan(const void* qkv, int64_t ldq, const void* b
 extern "C" int b2tts_matrix_memory_scan(const void* q, const void* k, const void* v, const void* ig, const void* fg, int64_t ldu,
                                         const float* i_bias, const float* f_bias, float cap, float* state, float* state_nm,
                                         float* gates, float* out, const int32_t* seq_start, const int32_t* seq_pos0,
-                                        const int32_t* seq_len, const int32_t* seq_slot, int n_seqs, int heads, int dim,
-                                        int vdim, int dtype, void* stream) {
+                                        const int32_t* seq_len, const int32_t* seq_slot, int n_tokens, int n_seqs, int heads,
+                                        int dim, int vdim, int dtype, void* stream) {
   SCAN_COMMON_CHECKS("matrix_memory_scan");
+  if (n_tokens <= 0) return B2TTS_OK;
   B2_REQUIRE(q && k && v && ig && fg && i_bias && f_bias && state_nm && gates && cap > 0.f, B2TTS_EINVAL,
              "matrix_memory_scan: null pointer or cap <= 0");
   B2_REQUIRE(dim <= SCAN_PER * 32, B2TTS_EUNSUPPORTED, "matrix_memory_scan: key size %d above %d", dim, SCAN_PER * 32);
@@ -371,14 +375,16 @@ extern "C" int b2tts_matrix_memory_scan(const void* q, const void* k, const void
   const float qscale = 1.0f / sqrtf(static_cast<float>(dim));
   const dim3 ggrid(heads, n_seqs);
   const int gthreads = 32;
-  if (dtype == B2TTS_DTYPE_BF16)
+  if (dtype == B2TTS_DTYPE_BF16) {
+    launch_coef<__nv_bfloat16>(ig, fg, ldu, i_bias, f_bias, gates, n_tokens, heads, 2, st, cap);
     matrix_memory_gates_kernel<__nv_bfloat16><<<ggrid, gthreads, 0, st>>>(static_cast<const __nv_bfloat16*>(k),
-        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(ig), static_cast<const __nv_bfloat16*>(fg), ldu, i_bias,
-        f_bias, cap, qscale, state_nm, gates, seq_start, seq_pos0, seq_len, seq_slot, heads, dim);
-  else
-    matrix_memory_gates_kernel<float><<<ggrid, gthreads, 0, st>>>(static_cast<const float*>(k), static_cast<const float*>(q),
-        static_cast<const float*>(ig), static_cast<const float*>(fg), ldu, i_bias, f_bias, cap, qscale, state_nm, gates, seq_start,
-        seq_pos0, seq_len, seq_slot, heads, dim);
+        static_cast<const __nv_bfloat16*>(q), ldu, qscale, state_nm, gates, seq_start, seq_pos0, seq_len, seq_slot, heads, dim);
+  } else {
+    launch_coef<float>(ig, fg, ldu, i_bias, f_bias, gates, n_tokens, heads, 2, st, cap);
+    matrix_memory_gates_kernel<float><<<ggrid, gthreads, 0, st>>>(static_cast<const float*>(k), static_cast<const float*>(q), ldu, qscale,
+                                                                 state_nm, gates, seq_start, seq_pos0, seq_len, seq_slot, heads, dim);
+  }
+  count_launch();
   B2_CHECK_LAUNCH("matrix_memory_gates");
   ScanArgs a{};
   a.q = q; a.ldq = ldu; a.k = k; a.ldk = ldu; a.v = v; a.ldv = ldu;
