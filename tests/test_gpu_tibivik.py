@@ -268,7 +268,9 @@ CUTS = [1, 2, 3, 7, 1, 1, 12, 2, 4]          # 33 tokens
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 4e-2)])
 @pytest.mark.parametrize("ssm", [dict(), dict(heads=4, groups=2, norm_groups=4, conv=2, state=5, vdim=3),
-                                 dict(heads=2, groups=2, norm_groups=2, conv=1, state=16, vdim=130)])
+                                 dict(heads=2, groups=2, norm_groups=2, conv=1, state=16, vdim=130),
+                                 dict(heads=2, groups=1, norm_groups=1, conv=4, state=100, vdim=40),     # four lanes per column
+                                 dict(heads=2, groups=2, norm_groups=1, conv=3, state=200, vdim=24)])    # eight lanes per column
 def test_state_space_mixer_in_portions_through_reused_slots(dtype, tol, ssm):
     from nano_qwen3tts_vllm_b200.config import TibivikConfig
     from nano_qwen3tts_vllm_b200.models.tibivik import StateSpaceMixer
@@ -303,7 +305,12 @@ def test_state_space_mixer_in_portions_through_reused_slots(dtype, tol, ssm):
                                                          window=dict(heads=2, kv_heads=2, dim=6, vdim=6, mask={"size": 4}, scale=0.5,
                                                                      rot={"dims": 6, "base": 17.0}))),
                                        ("parallel_2", dict(delta=dict(heads=3, kv_heads=3, dim=5, vdim=140, conv=2),
-                                                           chunk=dict(heads=2, kv_heads=2, dim=7, vdim=9, mask={"size": 16}, scale=0.4)))])
+                                                           chunk=dict(heads=2, kv_heads=2, dim=7, vdim=9, mask={"size": 16}, scale=0.4))),
+                                       # key sizes that put four and eight lanes on a value column of the recurrences
+                                       ("parallel", dict(memory=dict(heads=2, dim=96, vdim=40, gate_cap=6.0))),
+                                       ("parallel", dict(memory=dict(heads=1, dim=256, vdim=20, gate_cap=6.0))),
+                                       ("parallel_2", dict(delta=dict(heads=4, kv_heads=2, dim=128, vdim=36, conv=3))),
+                                       ("parallel_2", dict(delta=dict(heads=2, kv_heads=1, dim=130, vdim=33, conv=4)))])
 def test_parallel_mixers_each_branch_in_portions_through_reused_slots(dtype, tol, kind, over):
     from nano_qwen3tts_vllm_b200.config import TibivikConfig
     from nano_qwen3tts_vllm_b200.models.tibivik import TibivikForCausalLM
