@@ -112,7 +112,8 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int b = tok_seq[t];
   T* orow = out + (t * H + h0) * dv;                  // the REP heads' outputs are adjacent
-  if (only_single && seq_len[b] > 1) return;          // the tensor-core kernel owns prompt portions
+  if ((only_single & 1) && seq_len[b] > 1) return;    // the tensor-core kernel owns prompt portions
+  if ((only_single & 2) && seq_len[b] == 1) return;   // the row-splitting kernel owns one-token rows
   if (seq_len[b] <= 0) {                              // padding row
     for (int c = threadIdx.x; c < REP * dv; c += blockDim.x) orow[c] = from_f<T>(0.f);
     return;
@@ -245,6 +246,192 @@ static void launch_sink_plain_rep(int rep, cudaStream_t st, const void* q, const
   else if (rep % 2 == 0) launch_sink_plain<T, 2>(SINK_PLAIN_ARGS);
   else launch_sink_plain<T, 1>(SINK_PLAIN_ARGS);
 #undef SINK_PLAIN_ARGS
+}
+
+// ------------------------------------------------------------------ one-token rows: the lanes split a cached row
+// One CTA of eight warps per (sequence with ONE new token, REP query heads of a key/value group).  LPK lanes read one key
+// row, 16 bytes each (N elements; d = dv = LPK * N), so a warp-wide load is contiguous and covers 32 / LPK keys; a lane
+// keeps its slice of the REP queries (times scale * log2 e) and of the REP accumulators in registers.  Four key steps
+// (K and V pieces of four keys per lane group) are in flight before the first is used.  A score is the slice's dot product
+// summed over the LPK lanes by shuffles; every lane group keeps a running maximum and denominator per head (base 2), the
+// groups of a warp are merged by shuffles and the warps through shared memory, where the sink joins the denominator.
+constexpr int SD_WARPS = 8, SD_AHEAD = 4;
+
+template <typename T, int LPK, int REP>
+__global__ void __launch_bounds__(SD_WARPS * 32)
+sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
+                        const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
+                        const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int64_t bt_stride,
+                        const float* __restrict__ sink, const T* __restrict__ gate, int64_t ldg, int H, int G, int page,
+                        int mask_kind, int mask, float scale) {
+  constexpr int N = Vec16<T>::N, D = LPK * N, KPW = 32 / LPK;
+  constexpr float LOG2E = 1.4426950408889634f;
+  __shared__ float part[SD_WARPS][REP][D + 2];
+  const int b = blockIdx.x;
+  if (seq_len[b] != 1) return;
+  const int h0 = blockIdx.y * REP, g = h0 / (H / G);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % LPK, kg = lane / LPK;
+  const size_t t = seq_start[b];
+  const int i = seq_pos0[b];
+  int lo = 0;
+  if (mask > 0) lo = mask_kind == 0 ? max(0, i - mask + 1) : (i / mask) * mask;
+  const int32_t* bt = block_tables + static_cast<int64_t>(b) * bt_stride;
+  const size_t row = static_cast<size_t>(G) * D;          // elements of a cached row (K and V alike: dv = d)
+  float qv[REP][N], acc[REP][N], m[REP], l[REP];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    const T* qr = q + (t * H + h0 + r) * D + sub * N;
+#pragma unroll
+    for (int e = 0; e < N; ++e) { qv[r][e] = to_f(qr[e]) * (scale * LOG2E); acc[r][e] = 0.f; }
+    m[r] = -1e30f; l[r] = 0.f;
+  }
+  auto unpack = [](const uint4& raw, float* f) {
+    if constexpr (N == 8) {
+      f[0] = bf16lo(raw.x); f[1] = bf16hi(raw.x); f[2] = bf16lo(raw.y); f[3] = bf16hi(raw.y);
+      f[4] = bf16lo(raw.z); f[5] = bf16hi(raw.z); f[6] = bf16lo(raw.w); f[7] = bf16hi(raw.w);
+    } else {
+      f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+    }
+  };
+  constexpr int STEP = SD_WARPS * KPW;                     // keys the CTA takes per step
+  for (int j0 = lo; j0 <= i; j0 += STEP * SD_AHEAD) {
+    uint4 kraw[SD_AHEAD], vraw[SD_AHEAD];
+    bool ok[SD_AHEAD];
+#pragma unroll
+    for (int u = 0; u < SD_AHEAD; ++u) {
+      const int j = j0 + u * STEP + warp * KPW + kg;
+      ok[u] = j <= i;
+      kraw[u] = vraw[u] = make_uint4(0, 0, 0, 0);
+      if (ok[u]) {
+        const int pg = j / page;
+        const size_t slot = static_cast<size_t>(bt[pg]) * page + (j - pg * page);
+        kraw[u] = ldg_v4(k_cache + slot * row + g * D + sub * N);
+        vraw[u] = ldg_v4(v_cache + slot * row + g * D + sub * N);
+      }
+    }
+    float sc[SD_AHEAD][REP];
+#pragma unroll
+    for (int u = 0; u < SD_AHEAD; ++u) {
+      float f[N];
+      unpack(kraw[u], f);
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        float s = 0.f;
+#pragma unroll
+        for (int e = 0; e < N; ++e) s += f[e] * qv[r][e];
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        sc[u][r] = ok[u] ? s : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      float mx = sc[0][r];
+#pragma unroll
+      for (int u = 1; u < SD_AHEAD; ++u) mx = fmaxf(mx, sc[u][r]);
+      const float m_new = fmaxf(m[r], mx);                 // finite: m starts finite
+      const float corr = exp2f(m[r] - m_new);
+      m[r] = m_new;
+      l[r] *= corr;
+#pragma unroll
+      for (int e = 0; e < N; ++e) acc[r][e] *= corr;
+#pragma unroll
+      for (int u = 0; u < SD_AHEAD; ++u) sc[u][r] = exp2f(sc[u][r] - m_new);
+    }
+#pragma unroll
+    for (int u = 0; u < SD_AHEAD; ++u) {
+      float f[N];
+      unpack(vraw[u], f);
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        l[r] += sc[u][r];
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[r][e] += sc[u][r] * f[e];
+      }
+    }
+  }
+  // the lane groups of the warp
+#pragma unroll
+  for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m[r], o), l_o = __shfl_xor_sync(0xffffffffu, l[r], o);
+      const float m_new = fmaxf(m[r], m_o);
+      const float ca = exp2f(m[r] - m_new), cb = exp2f(m_o - m_new);
+      l[r] = l[r] * ca + l_o * cb;
+#pragma unroll
+      for (int e = 0; e < N; ++e) acc[r][e] = acc[r][e] * ca + __shfl_xor_sync(0xffffffffu, acc[r][e], o) * cb;
+      m[r] = m_new;
+    }
+  }
+  if (kg == 0) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+#pragma unroll
+      for (int e = 0; e < N; ++e) part[warp][r][sub * N + e] = acc[r][e];
+      if (sub == 0) { part[warp][r][D] = m[r]; part[warp][r][D + 1] = l[r]; }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    const int h = h0 + r;
+    float mm = sink != nullptr ? sink[h] * LOG2E : -1e30f;
+    const float sk = mm;
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) mm = fmaxf(mm, part[w][r][D]);
+    float den = sink != nullptr ? exp2f(sk - mm) : 0.f;
+    float cw[SD_WARPS];
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) {
+      cw[w] = exp2f(part[w][r][D] - mm);
+      den += cw[w] * part[w][r][D + 1];
+    }
+    float gv = 1.f;
+    if (gate != nullptr) gv = sigmoid_f(to_f(gate[t * ldg + h]));
+    const float inv = gv / den;
+    T* orow = out + (t * H + h) * D;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < SD_WARPS; ++w) o += cw[w] * part[w][r][c];
+      orow[c] = from_f<T>(o * inv);
+    }
+  }
+}
+
+template <typename T, int LPK>
+static void launch_sink_decode(int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
+                               const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
+                               int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int page,
+                               int mask_kind, int mask, float scale) {
+#define SD_GO(REP) sink_attn_decode_kernel<T, LPK, REP><<<dim3(n_seqs, H / REP), SD_WARPS * 32, 0, st>>>(static_cast<const T*>(q), \
+      static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, sink, \
+      static_cast<const T*>(gate), ldg, H, G, page, mask_kind, mask, scale)
+  if (rep % 4 == 0 && LPK * Vec16<T>::N <= 128) SD_GO(4);
+  else if (rep % 2 == 0) SD_GO(2);
+  else SD_GO(1);
+#undef SD_GO
+}
+
+// the row-splitting kernel takes d = dv = LPK * (16 / sizeof(T)) with LPK in {4, 8, 16, 32}
+template <typename T>
+static bool launch_sink_decode_any(int d, int dv, int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
+                                   const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
+                                   int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G,
+                                   int page, int mask_kind, int mask, float scale) {
+  constexpr int N = Vec16<T>::N;
+  if (d != dv || d % N != 0) return false;
+#define SD_ARGS rep, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, n_seqs, H, G, page, mask_kind, mask, scale
+  switch (d / N) {
+    case 4: launch_sink_decode<T, 4>(SD_ARGS); return true;
+    case 8: launch_sink_decode<T, 8>(SD_ARGS); return true;
+    case 16: launch_sink_decode<T, 16>(SD_ARGS); return true;
+    case 32: launch_sink_decode<T, 32>(SD_ARGS); return true;
+    default: return false;
+  }
+#undef SD_ARGS
 }
 
 // ------------------------------------------------------------------ prompt portions on the tensor cores (bf16)
@@ -516,13 +703,27 @@ extern "C" int b2tts_sink_attn(const void* q, const void* k_cache, const void* v
     if (e != cudaSuccess) return cuda_fail(e, "sink_attn (tensor cores)");
     B2_CHECK_LAUNCH("sink_attn (tensor cores)");
   }
+  // one-token rows: the row-splitting kernel where the head size fits it (path 1 keeps everything in the plain kernel)
+  bool split = false;
+  if (path != 1 && aligned16(q) && n_seqs > 0) {
+    if (dtype == B2TTS_DTYPE_BF16)
+      split = launch_sink_decode_any<__nv_bfloat16>(dim, vdim, heads / kv_heads, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
+                                                    block_tables, bt_stride, sink, gate, ldg, n_seqs, heads, kv_heads, page, mask_kind,
+                                                    mask, scale);
+    else
+      split = launch_sink_decode_any<float>(dim, vdim, heads / kv_heads, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
+                                            block_tables, bt_stride, sink, gate, ldg, n_seqs, heads, kv_heads, page, mask_kind, mask,
+                                            scale);
+    if (split) B2_CHECK_LAUNCH("sink_attn (one-token rows)");
+  }
+  const int skip = (use_mma ? 1 : 0) | (split ? 2 : 0);
   if (dtype == B2TTS_DTYPE_BF16)
     launch_sink_plain_rep<__nv_bfloat16>(heads / kv_heads, st, q, k_cache, v_cache, out, tok_seq, positions, seq_len, block_tables,
                                          bt_stride, sink, gate, ldg, n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale,
-                                         use_mma ? 1 : 0);
+                                         skip);
   else
     launch_sink_plain_rep<float>(heads / kv_heads, st, q, k_cache, v_cache, out, tok_seq, positions, seq_len, block_tables, bt_stride,
-                                 sink, gate, ldg, n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, 0);
+                                 sink, gate, ldg, n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, skip);
   B2_CHECK_LAUNCH("sink_attn");
   return B2TTS_OK;
 }

@@ -200,6 +200,18 @@ def test_tensor_core_sink_attention_against_plain_model_and_plain_kernel(nat, H,
     assert rel(plain, ref) < 1.5e-2 and rel(tc, ref) < 1.5e-2
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 1.5e-2)])
+@pytest.mark.parametrize("H,G,d", [(16, 8, 128), (8, 2, 32), (4, 1, 256), (3, 3, 64), (6, 1, 16), (2, 1, 64)])
+@pytest.mark.parametrize("kind,mask", [("window", 1), ("window", 37), ("window", 300), ("chunk", 1), ("chunk", 64), ("chunk", 129)])
+def test_one_token_rows_where_lanes_split_a_cached_row(nat, dtype, tol, H, G, d, kind, mask):
+    """Sequences with ONE new token at contexts from 0 to several hundred keys (head sizes the row-splitting kernel takes,
+    1 / 2 / 4 heads of a group per CTA), beside a prompt portion in the same launch; against the model and the plain kernel."""
+    seqs = [(0, 1), (1, 1), (63, 1), (64, 1), (300, 1), (20, 5), (511, 1), (128, 1)]
+    out, ref = _attn_case(nat, H, G, d, d, kind, mask, 16, seqs, dtype, gate=(H % 3 == 0), seed=mask + d)
+    plain, _ = _attn_case(nat, H, G, d, d, kind, mask, 16, seqs, dtype, gate=(H % 3 == 0), seed=mask + d, path=nat.SINK_ATTN_PLAIN)
+    assert rel(out, ref) < tol and rel(plain, ref) < tol
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("page", [16, 64])
 @pytest.mark.parametrize("kind,mask", [("window", 33), ("window", 64), ("window", 200), ("chunk", 33), ("chunk", 64), ("chunk", 200)])
