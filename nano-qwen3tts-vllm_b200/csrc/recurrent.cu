@@ -58,14 +58,14 @@ __device__ __forceinline__ float slice_sum(float v) {
 //   SCAN_DELTA    S <- c0 S; u = c1 (v - S^T k^); S <- S + k^ u^T;      out = S^T q^ * qscale      (k^, q^: unit vectors)
 // RS = threads per value column = ceil(d / 32) rounded up to a power of two; the CTA is RS warps and owns 32 columns.  A
 // warp holds 32 / RS columns; thread (slice, column) keeps rows slice * 32 .. + 31 of its column in registers for the
-// whole portion.  Thread i stages element i of the token's k and q (zero beyond d) in shared memory; the loads run
-// SCAN_DEPTH tokens ahead through registers, so a token waits for the barrier and its own arithmetic only.
+// whole portion.  Thread i stages element i of a token's k and q (zero beyond d) in shared memory, SCAN_DEPTH tokens at a
+// time; the loads run a group of tokens ahead through registers, so a token waits for its own arithmetic only.
 template <typename T, int KIND, int RS>
 __global__ void __launch_bounds__(32 * RS)
 scan_kernel(const ScanArgs a) {
   constexpr int CW = 32 / RS;                              // columns per warp
   constexpr int DP = RS * SCAN_ROWS;                       // padded key size = threads
-  __shared__ __align__(16) float vec[2][2][DP];            // [buffer][k | q][row]
+  __shared__ __align__(16) float vec[2][SCAN_DEPTH][2][DP];   // [buffer][token of the group][k | q][row]
   const int b = blockIdx.z, h = blockIdx.y;
   const int len = a.seq_len[b];
   if (len <= 0) return;
@@ -107,18 +107,27 @@ scan_kernel(const ScanArgs a) {
   };
 #pragma unroll
   for (int u = 0; u < SCAN_DEPTH; ++u) fetch(u, u);
-  for (int t0 = 0; t0 < len; t0 += SCAN_DEPTH) {
+  // tokens go in groups of SCAN_DEPTH: the group's vectors are staged at once (one barrier per group, two buffers), the
+  // next group's loads are issued, then the group's tokens are walked without a barrier between them
+  for (int t0 = 0, grp = 0; t0 < len; t0 += SCAN_DEPTH, grp ^= 1) {
+    float vals[SCAN_DEPTH], cs[SCAN_DEPTH][3];
+#pragma unroll
+    for (int u = 0; u < SCAN_DEPTH; ++u) {
+      vec[grp][u][0][tid] = to_f(rk[u]);
+      vec[grp][u][1][tid] = to_f(rq[u]);
+      vals[u] = to_f(rv[u]);
+      cs[u][0] = rc[u][0]; cs[u][1] = rc[u][1]; cs[u][2] = rc[u][2];
+    }
+#pragma unroll
+    for (int u = 0; u < SCAN_DEPTH; ++u) fetch(u, t0 + SCAN_DEPTH + u);
+    __syncthreads();                                       // group staged; the other buffer's readers finished a group ago
 #pragma unroll
     for (int u = 0; u < SCAN_DEPTH; ++u) {
       const int t = t0 + u;
       if (t >= len) break;                                 // uniform over the CTA
-      float* ks = vec[u & 1][0];
-      float* qs = vec[u & 1][1];
-      ks[tid] = to_f(rk[u]);
-      qs[tid] = to_f(rq[u]);
-      const float val = to_f(rv[u]), c0 = rc[u][0], c1 = rc[u][1], c2 = rc[u][2];
-      fetch(u, t + SCAN_DEPTH);
-      __syncthreads();                                     // token t is staged; the other buffer is free again
+      const float* ks = vec[grp][u][0];
+      const float* qs = vec[grp][u][1];
+      const float val = vals[u], c0 = cs[u][0], c1 = cs[u][1], c2 = cs[u][2];
       float kr[SCAN_ROWS];
 #pragma unroll
       for (int x = 0; x < SCAN_ROWS; x += 4) {
