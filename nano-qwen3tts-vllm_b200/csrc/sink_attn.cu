@@ -7,6 +7,10 @@
 // Both masks are a lower bound on j, so one kernel serves them.  The sink has no key and no value and is not scaled.  An
 // optional per-head gate multiplies the head's output by sigmoid(gate[t, h]).
 //
+// Three kernels share a launch: prompt portions in bf16 with head sizes 32..128 x 64, 128 run on the tensor cores
+// (sink_attn_mma_kernel), rows with ONE new token and a head size of 4, 8, 16 or 32 16-byte pieces (d = dv) in a kernel whose
+// lanes split a cached row (sink_attn_decode_kernel), everything else in the plain kernel; each skips the rows of the others.
+//
 // Plain kernel (bf16 or float, any head size up to 256): one CTA of four warps per token and 1, 2 or 4 query heads of one
 // key/value group, so a cached row is loaded once for all of them.  A warp takes 32-key tiles: each lane scores one key
 // against the queries held in shared memory (float accumulation), the warp keeps a running maximum and denominator per
