@@ -480,22 +480,96 @@ gated_group_norm_vec4_kernel(const float* __restrict__ y, const T* __restrict__ 
     }
     if (gate_first) { v.x *= g.x; v.y *= g.y; v.z *= g.z; v.w *= g.w; }
   };
+  // a group of up to GN_KEEP vectors per thread stays in registers between the sum of squares and the scaled write
+  constexpr int GN_KEEP = 4;
+  const bool keep = gs <= 4 * GN_KEEP * static_cast<int>(blockDim.x);
+  float4 kv[GN_KEEP], kg[GN_KEEP];
   float ssq = 0.f;
-  for (int c = threadIdx.x * 4; c < gs; c += blockDim.x * 4) {
-    float4 v, g;
-    gated(c, v, g);
-    ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  if (keep) {
+#pragma unroll
+    for (int it = 0; it < GN_KEEP; ++it) {
+      const int c = (threadIdx.x + it * blockDim.x) * 4;
+      kv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+      kg[it] = kv[it];
+      if (c < gs) {
+        gated(c, kv[it], kg[it]);
+        ssq += kv[it].x * kv[it].x + kv[it].y * kv[it].y + kv[it].z * kv[it].z + kv[it].w * kv[it].w;
+      }
+    }
+  } else {
+    for (int c = threadIdx.x * 4; c < gs; c += blockDim.x * 4) {
+      float4 v, g;
+      gated(c, v, g);
+      ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
   }
   const float inv = 1.0f / sqrtf(block_sum(ssq, red) / static_cast<float>(gs) + eps);
   T* o = out + r * cols + c0;
-  for (int c = threadIdx.x * 4; c < gs; c += blockDim.x * 4) {
-    float4 v, g;
-    gated(c, v, g);
+  auto emit = [&](int c, const float4& v, const float4& g) {
     const int wc = (c0 + c) % w_len;                       // w_len is a multiple of four here
     const float4 ww = *reinterpret_cast<const float4*>(w + wc);
     float4 res = make_float4(v.x * inv * ww.x, v.y * inv * ww.y, v.z * inv * ww.z, v.w * inv * ww.w);
     if (!gate_first) { res.x *= g.x; res.y *= g.y; res.z *= g.z; res.w *= g.w; }
     store4<T>(o + c, res);
+  };
+  if (keep) {
+#pragma unroll
+    for (int it = 0; it < GN_KEEP; ++it) {
+      const int c = (threadIdx.x + it * blockDim.x) * 4;
+      if (c < gs) emit(c, kv[it], kg[it]);
+    }
+  } else {
+    for (int c = threadIdx.x * 4; c < gs; c += blockDim.x * 4) {
+      float4 v, g;
+      gated(c, v, g);
+      emit(c, v, g);
+    }
+  }
+}
+
+// Small groups (a head each): one CTA per row, a warp per group in turn, the group's values in registers, no barrier.
+constexpr int GNW_KEEP = 4;                                // groups of up to 4 * GNW_KEEP * 32 = 512 values
+
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+gated_group_norm_warp_kernel(const float* __restrict__ y, const T* __restrict__ gate, int64_t ldg, const float* __restrict__ w,
+                             int w_len, int groups, int act, int gate_first, float eps, T* __restrict__ out, int cols) {
+  const size_t r = blockIdx.x;
+  const int gs = cols / groups, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int grp = threadIdx.x >> 5; grp < groups; grp += nw) {
+    const int c0 = grp * gs;
+    const float* yr = y + r * cols + c0;
+    const T* gr = gate != nullptr ? gate + r * ldg + c0 : nullptr;
+    float4 kv[GNW_KEEP], kg[GNW_KEEP];
+    float ssq = 0.f;
+#pragma unroll
+    for (int it = 0; it < GNW_KEEP; ++it) {
+      const int c = (lane + it * 32) * 4;
+      kv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+      kg[it] = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (c < gs) {
+        kv[it] = *reinterpret_cast<const float4*>(yr + c);
+        if (gr != nullptr) {
+          const float4 z = load4<T>(gr + c);
+          if (act == 0) kg[it] = make_float4(sigmoid_f(z.x), sigmoid_f(z.y), sigmoid_f(z.z), sigmoid_f(z.w));
+          else kg[it] = make_float4(silu_f(z.x), silu_f(z.y), silu_f(z.z), silu_f(z.w));
+        }
+        if (gate_first) { kv[it].x *= kg[it].x; kv[it].y *= kg[it].y; kv[it].z *= kg[it].z; kv[it].w *= kg[it].w; }
+        ssq += kv[it].x * kv[it].x + kv[it].y * kv[it].y + kv[it].z * kv[it].z + kv[it].w * kv[it].w;
+      }
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ssq) / static_cast<float>(gs) + eps);
+    T* o = out + r * cols + c0;
+#pragma unroll
+    for (int it = 0; it < GNW_KEEP; ++it) {
+      const int c = (lane + it * 32) * 4;
+      if (c < gs) {
+        const float4 ww = *reinterpret_cast<const float4*>(w + (c0 + c) % w_len);
+        float4 res = make_float4(kv[it].x * inv * ww.x, kv[it].y * inv * ww.y, kv[it].z * inv * ww.z, kv[it].w * inv * ww.w);
+        if (!gate_first) { res.x *= kg[it].x; res.y *= kg[it].y; res.z *= kg[it].z; res.w *= kg[it].w; }
+        store4<T>(o + c, res);
+      }
+    }
   }
 }
 
@@ -660,6 +734,17 @@ extern "C" int b2tts_gated_group_norm(const float* y, const void* gate, int64_t 
   const dim3 grid(rows, groups);
   const bool vec4 = gs % 4 == 0 && w_len % 4 == 0 && ldg % 4 == 0 && aligned16(y) && aligned16(w) && aligned16(out) &&
                     (!gate || aligned16(gate));
+  if (vec4 && groups > 1 && gs <= 4 * GNW_KEEP * 32) {
+    const int threads = 32 * std::min(groups, ROW_THREADS / 32);
+    if (dtype == B2TTS_DTYPE_BF16)
+      gated_group_norm_warp_kernel<__nv_bfloat16><<<rows, threads, 0, st>>>(y, static_cast<const __nv_bfloat16*>(gate), ldg, w, w_len,
+          groups, gate_act, gate_first, eps, static_cast<__nv_bfloat16*>(out), cols);
+    else
+      gated_group_norm_warp_kernel<float><<<rows, threads, 0, st>>>(y, static_cast<const float*>(gate), ldg, w, w_len, groups, gate_act,
+                                                                   gate_first, eps, static_cast<float*>(out), cols);
+    B2_CHECK_LAUNCH("gated_group_norm");
+    return B2TTS_OK;
+  }
   if (vec4) {
     const int threads = std::min(ROW_THREADS, (gs / 4 + 31) / 32 * 32);
     if (dtype == B2TTS_DTYPE_BF16)
