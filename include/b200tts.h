@@ -455,13 +455,14 @@ B2TTS_API int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, cons
                                         const int32_t* block_tables, int bt_stride, const float* r1, const float* r2,
                                         const float* pb, int n_seqs, int max_new, int heads, int kv_heads, int dim, int vdim,
                                         int page, int window, float scale, int dtype, void* stream);
-/* Top-k router, in float.  softmax_chosen == 0: scores = sigmoid(h router^T), top_w = score / (sum of the chosen + 1e-20)
- * * scale.  softmax_chosen == 1: scores = h router^T + bias (bias may be null), top_w = softmax over the chosen scores only,
- * * scale.  top_idx [n, top] the `top` largest (ties: lower index); then the (token, choice) pairs grouped by expert:
+/* Top-k router, in float.  mode 0: scores = sigmoid(h router^T), top_w = score / (sum of the chosen + 1e-20) * scale.
+ * mode 1: scores = h router^T + bias (bias may be null), top_w = softmax over the chosen scores only, * scale.
+ * mode 2: scores = softmax(h router^T) over all experts, the choice is made on score + bias, top_w = the chosen scores
+ * * scale (not renormalised).  top_idx [n, top] the `top` largest (ties: lower index); then the (token, choice) pairs grouped by expert:
  * offsets [experts + 1], sorted_pair [n * top] (pair = token * top + choice; order inside a group unspecified). */
 B2TTS_API int b2tts_moe_route(const void* h, const float* router, int32_t* top_idx, float* top_w, int32_t* offsets,
                               int32_t* sorted_pair, int n_tokens, int cols, int experts, int top, float scale,
-                              const float* bias, int softmax_chosen, int dtype, void* stream);
+                              const float* bias, int mode, int dtype, void* stream);
 /* C[out_row(s), :] = act(A[in_row(s), :] W[e]^T) for s in offsets[e] .. offsets[e+1], W [experts, n, k];
  * in_row(s) = sorted_pair[s] / top if in_by_token else s; out_row(s) = sorted_pair[s] if out_by_pair else s;
  * act 0 = none, 1 = squared ReLU; float accumulation. */
@@ -487,7 +488,7 @@ B2TTS_API int b2tts_latent_prep(const void* u, int64_t ldu, int q_off, int kv_of
                                 const int32_t* slot_mapping, void* cache, int n_tokens, int q_rank, int kv_rank, int rot_dim,
                                 int rot_dims, float eps, int dtype, void* stream);
 /* Multi-query softmax attention over cached rows [c | kr] with a sink in the denominator; see csrc/latent_attn.cu.
- * ql: absorbed queries (element (t, h, :) at ql + t * ql_tok + h * ql_head, kv_rank numbers), qr: rotary query parts, not yet
+ * sink null: an ordinary softmax.  ql: absorbed queries (element (t, h, :) at ql + t * ql_tok + h * ql_head, kv_rank numbers), qr: rotary query parts, not yet
  * turned (rot_dim numbers), out: weighted latent sums (kv_rank numbers), strides in elements.  window 0 = every earlier key.
  * path 0 = choose, 1 = the plain kernel, 2 = the tensor-core kernel with two key stages (bf16; fails if the sizes do not
  * fit it), 3 = the tensor-core kernel with one key stage and two CTAs per SM. */
@@ -539,23 +540,29 @@ B2TTS_API int b2tts_stream_gather_norm(const float* xs, const int32_t* rows_idx,
 /* Row t of the merged projection u (row stride ldu): q = u[q_off : +heads*dim] + q_bias, k = u[k_off : +kv_heads*dim] + k_bias,
  * v = u[v_off : +kv_heads*vdim] + v_bias, or v = k as it stands here when v_off < 0 (biases may be null).  With q_norm_w and
  * k_norm_w, q and k are divided by the root mean square of their whole projection and multiplied by the weights.  With
- * rot_dims > 0, coordinate i < rot_dims/2 of every head is paired with i + rot_dims/2 and turned by positions[t] * freq[i].
- * q -> q_out[t]; k, v -> the caches at slot_mapping[t]. */
+ * rot_dims > 0, coordinate i < rot_dims/2 of every head is paired with i + rot_dims/2 (interleaved != 0: coordinate 2i with
+ * 2i + 1) and turned by positions[t] * freq[i].  q -> q_out[t]; k, v -> the caches at slot_mapping[t]; with both caches null
+ * only q is made (a layer that reads the keys and values another layer wrote).  v_heads: value heads projected and cached
+ * (kv_heads unless several key maps share one set of values). */
 B2TTS_API int b2tts_attn_prep(const void* u, int64_t ldu, int q_off, int k_off, int v_off, const float* q_bias, const float* k_bias,
                               const float* v_bias, const float* q_norm_w, const float* k_norm_w, const float* freq, int rot_dims,
                               const int32_t* positions, const int32_t* slot_mapping, void* q_out, void* k_cache, void* v_cache,
-                              int n_tokens, int heads, int kv_heads, int dim, int vdim, float eps, int dtype, void* stream);
+                              int n_tokens, int heads, int kv_heads, int dim, int vdim, float eps, int interleaved, int v_heads,
+                              int dtype, void* stream);
 /* Softmax attention with exp(sink[h]) added to the denominator (sink null: none) over the paged cache, this step's keys
  * included.  Token i sees key j <= i with j >= max(0, i - mask + 1) (mask_kind 0, a sliding window) or j >= floor(i / mask) *
- * mask (mask_kind 1, chunks counted from position 0); mask <= 0: every j <= i.  gate (optional): element (t, h) at
+ * mask (mask_kind 1, chunks counted from position 0); mask <= 0: every j <= i.  keep_first F > 0: keys j < F stay visible
+ * behind the mask.  softcap c > 0: a scaled score s becomes c tanh(s / c).  v_heads: value heads in v_cache, key head g reads
+ * value head g mod v_heads (v_heads == kv_heads: one each).  gate (optional): element (t, h) at
  * gate[t * ldg + h]; the head's output is multiplied by its sigmoid.  q [n, heads*dim], out [n, heads*vdim].  max_new >= every
  * seq_len[b].  path 0 = choose (bf16 prompt portions with head sizes the tensor-core kernel is built for run there, everything
  * else in the plain kernel), 1 = the plain kernel, 2 = the tensor-core kernel for prompt portions (fails if the sizes do not fit). */
 B2TTS_API int b2tts_sink_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* tok_seq,
                               const int32_t* positions, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
                               const int32_t* block_tables, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg,
-                              int n_tokens, int n_seqs, int max_new, int heads, int kv_heads, int dim, int vdim, int page,
-                              int mask_kind, int mask, float scale, int dtype, int path, void* stream);
+                              int n_tokens, int n_seqs, int max_new, int heads, int kv_heads, int v_heads, int dim, int vdim,
+                              int page, int mask_kind, int mask, int keep_first, float softcap, float scale, int dtype, int path,
+                              void* stream);
 /* out[t, c] = act(bias[c] + sum_j w[c, j] * u(position(t) - taps + 1 + j)[c_off + c]) for c < channels (act 0: none, 1: SiLU;
  * bias may be null).  Earlier positions come from this step's rows, from state [slots, taps-1, channels] (the sequence's last
  * rows, oldest first, advanced by this call) or are zero before position 0.  max_new >= every seq_len[b] (0: unknown). */
@@ -593,6 +600,31 @@ B2TTS_API int b2tts_matrix_memory_scan(const void* q, const void* k, const void*
                                        float* gates, float* out, const int32_t* seq_start, const int32_t* seq_pos0,
                                        const int32_t* seq_len, const int32_t* seq_slot, int n_tokens, int n_seqs, int heads, int dim,
                                        int vdim, int dtype, void* stream);
+
+/* Gated linear attention per head, state [slots, heads, dim, vdim] float: decay[t, h, i] = sigmoid(z[t, h * dim + i] + z_bias[h * dim
+ * + i])^(1 / tau) (in float; z_bias may be null); S[i, :] <- decay[i] S[i, :] + k[i] v^T; out[t, h] = S^T q * dim^(-1/2).  q, k, z
+ * [rows, heads*dim] and v [rows, heads*vdim] with their own row strides; decay [rows, heads*dim] float is scratch. */
+B2TTS_API int b2tts_gated_linear_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const void* z,
+                                      int64_t ldz, const float* z_bias, float tau, float* decay, float* state, float* out,
+                                      const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
+                                      const int32_t* seq_slot, int n_tokens, int n_seqs, int heads, int dim, int vdim, int dtype,
+                                      void* stream);
+
+/* ---- decoders whose sublayers are normed on the way in and on the way out with single-gain RMS norms (csrc/sandwich_ops.cu).
+ * x[r] (init != 0: starting from zero) += g_out[0] * N(y[r]); h[r] = g_in[0] * N(x[r]) when h != null; N(v) = v / sqrt(mean(v^2) + eps).
+ * y = a[a_index ? a_index[r] : r] (a table of a_rows rows when indexed), or, with wa and wb, branch_scale * (N(a) * wa + N(b) * wb);
+ * plus sum_k zw[r, k] * (z_idx == null || z_idx[r, k] < n_real ? z[r * top + k] : hin[r]) in ascending k. */
+B2TTS_API int b2tts_sandwich_residual(float* x, const void* a, const int32_t* a_index, int a_rows, const void* b, const float* wa,
+                                      const float* wb, float branch_scale, const void* z, const float* zw, const int32_t* z_idx,
+                                      int top, int n_real, const void* hin, const float* g_out, const float* g_in, void* h,
+                                      int rows, int cols, int init, float eps, int dtype, void* stream);
+/* In place on rows of y: coef[0] N(y) + coef[1] N(y^2) + coef[2] N(y^3) + coef[3], powers element by element. */
+B2TTS_API int b2tts_polynorm(void* y, const float* coef, int rows, int cols, float eps, int dtype, void* stream);
+/* maps [rows, 2, heads, vdim]: out[r, h] = (maps[r, 0, h] - lambda * maps[r, 1, h]) / sqrt(mean over vdim of its square + eps) * mult. */
+B2TTS_API int b2tts_diff_combine(const void* maps, void* out, float lambda, float mult, int rows, int heads, int vdim, float eps,
+                                 int dtype, void* stream);
+/* In place: y <- cap * tanh(y / cap). */
+B2TTS_API int b2tts_tanh_cap(float* y, int64_t n, float cap, void* stream);
 
 #ifdef __cplusplus
 }

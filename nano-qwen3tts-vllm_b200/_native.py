@@ -101,8 +101,13 @@ def _load():
         "b2tts_embed_bigram_streams": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, P]),
         "b2tts_stream_mix_norm": (I, [P, P, P, F, F, P, P, P, P, P, I, I, I, F, I, P]),
         "b2tts_stream_gather_norm": (I, [P, P, P, P, P, I, I, I, F, I, P]),
-        "b2tts_attn_prep": (I, [P, L, I, I, I, P, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, P]),
-        "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, I, I, F, I, I, P]),
+        "b2tts_attn_prep": (I, [P, L, I, I, I, P, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, I, P]),
+        "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, I, I, I, I, F, F, I, I, P]),
+        "b2tts_gated_linear_scan": (I, [P, L, P, L, P, L, P, L, P, F, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
+        "b2tts_sandwich_residual": (I, [P, P, P, I, P, P, P, F, P, P, P, I, I, P, P, P, P, I, I, I, F, I, P]),
+        "b2tts_polynorm": (I, [P, P, I, I, F, I, P]),
+        "b2tts_diff_combine": (I, [P, P, F, F, I, I, I, F, I, P]),
+        "b2tts_tanh_cap": (I, [P, L, F, P]),
         "b2tts_short_conv_act": (I, [P, L, I, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, I, P]),
         "b2tts_gated_group_norm": (I, [P, P, L, P, I, I, I, I, F, P, I, I, I, P]),
         "b2tts_ssm_scan": (I, [P, L, P, L, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
@@ -776,16 +781,22 @@ def window_sigmoid_attn(q, k_cache, v_cache, out, lay, r1, r2, pb, heads, kv_hea
         scale, dt, _stream()), "window_sigmoid_attn")
 
 
-def moe_route(h, router, top_idx, top_w, offsets, sorted_pair, top, scale, bias=None, softmax_chosen=False):
-    """``softmax_chosen``: scores are the logits (+ ``bias``) and the weights their softmax over the chosen ones;
-    otherwise sigmoid scores divided by the sum of the chosen."""
+ROUTE_SIGMOID, ROUTE_SOFTMAX_CHOSEN, ROUTE_SOFTMAX_ALL = 0, 1, 2
+
+
+def moe_route(h, router, top_idx, top_w, offsets, sorted_pair, top, scale, bias=None, softmax_chosen=False, mode=None):
+    """``mode`` ROUTE_SIGMOID: sigmoid scores divided by the sum of the chosen; ROUTE_SOFTMAX_CHOSEN (= ``softmax_chosen``):
+    scores are the logits (+ ``bias``) and the weights their softmax over the chosen ones; ROUTE_SOFTMAX_ALL: scores are
+    the softmax over all logits, ``bias`` enters the choice only and the weights are the chosen scores as they are."""
+    if mode is None:
+        mode = ROUTE_SOFTMAX_CHOSEN if softmax_chosen else ROUTE_SIGMOID
     dt = _act(h, "h")
     _cuda(router, F32, "router")
     if bias is not None:
         _cuda(bias, F32, "bias")
     n, cols = h.shape
     _check(_load().b2tts_moe_route(h.data_ptr(), router.data_ptr(), top_idx.data_ptr(), top_w.data_ptr(), offsets.data_ptr(),
-                                   sorted_pair.data_ptr(), n, cols, router.shape[0], top, scale, _ptr(bias), int(softmax_chosen),
+                                   sorted_pair.data_ptr(), n, cols, router.shape[0], top, scale, _ptr(bias), int(mode),
                                    dt, _stream()), "moe_route")
 
 
@@ -842,7 +853,7 @@ def latent_attn(ql, ql_strides, qr, qr_strides, cache, out, out_strides, sink, f
             ws = torch.empty(lib_.b2tts_latent_attn_workspace_floats(lay.n_seqs, lay.max_new, heads, kv_rank, splits),
                              dtype=F32, device=cache.device)
     _check(lib_.b2tts_latent_attn(ql.data_ptr(), ql_strides[0], ql_strides[1], qr.data_ptr(), qr_strides[0], qr_strides[1],
-                                  cache.data_ptr(), out.data_ptr(), out_strides[0], out_strides[1], sink.data_ptr(), _ptr(freq),
+                                  cache.data_ptr(), out.data_ptr(), out_strides[0], out_strides[1], _ptr(sink), _ptr(freq),
                                   rot_mult, rot_dims, lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(),
                                   lay.block_tables.data_ptr(), lay.block_tables.stride(0), lay.n_seqs, lay.max_new, heads,
                                   kv_rank, rot_dim, page, window, scale, dt, path, splits, _ptr(ws), _stream()), "latent_attn")
@@ -939,17 +950,20 @@ def stream_gather_norm(xs, rows, in_w, norm_w, eps, dtype, out=None):
 
 
 def attn_prep(u, q_off, k_off, v_off, q_bias, k_bias, v_bias, q_norm_w, k_norm_w, freq, rot_dims, lay, q_out, k_cache, v_cache,
-              heads, kv_heads, dim, vdim, eps):
-    """Biases, whole-projection RMS norm and half-split rotation of q and k; k and v go to their cache slots
-    (``v_off`` < 0: the values are the keys as projected)."""
+              heads, kv_heads, dim, vdim, eps, interleaved=False, v_heads=None):
+    """Biases, whole-projection RMS norm and rotation of q and k (coordinate i with i + rot_dims/2, or, ``interleaved``, 2i
+    with 2i + 1); k and v go to their cache slots (``v_off`` < 0: the values are the keys as projected).  Without caches
+    (both None) only q is made: the layer reads keys and values another layer wrote."""
     dt = _act(q_out, "q_out")
-    assert u.dtype == q_out.dtype and u.stride(1) == 1 and k_cache.dtype == u.dtype and v_cache.dtype == u.dtype
+    assert u.dtype == q_out.dtype and u.stride(1) == 1
+    assert (k_cache is None and v_cache is None) or (k_cache.dtype == u.dtype and v_cache.dtype == u.dtype)
     for t in (q_bias, k_bias, v_bias, q_norm_w, k_norm_w, freq):
         assert t is None or (t.dtype == F32 and t.is_contiguous())
     _check(_load().b2tts_attn_prep(u.data_ptr(), u.stride(0), q_off, k_off, v_off, _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
                                    _ptr(q_norm_w), _ptr(k_norm_w), _ptr(freq), rot_dims, lay.positions.data_ptr(),
-                                   lay.slot_mapping.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
-                                   lay.n_tokens, heads, kv_heads, dim, vdim, eps, dt, _stream()), "attn_prep")
+                                   lay.slot_mapping.data_ptr(), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
+                                   lay.n_tokens, heads, kv_heads, dim, vdim, eps, int(interleaved),
+                                   kv_heads if v_heads is None else v_heads, dt, _stream()), "attn_prep")
 
 
 MASK_WINDOW, MASK_CHUNK = 0, 1
@@ -958,16 +972,20 @@ MASK_WINDOW, MASK_CHUNK = 0, 1
 SINK_ATTN_AUTO, SINK_ATTN_PLAIN, SINK_ATTN_TENSOR = 0, 1, 2
 
 
-def sink_attn(q, k_cache, v_cache, out, lay, sink, gate, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, path=SINK_ATTN_AUTO):
-    """``gate``: a column slice [n, heads] of the merged projection (or None)."""
+def sink_attn(q, k_cache, v_cache, out, lay, sink, gate, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, path=SINK_ATTN_AUTO,
+              v_heads=None, keep_first=0, softcap=0.0):
+    """``gate``: a column slice [n, heads] of the merged projection (or None).  ``sink`` None: an ordinary softmax.
+    ``v_heads``: value heads in the cache (key head g reads value head g mod v_heads; default ``kv_heads``);
+    ``keep_first``: keys below this position stay visible behind the mask; ``softcap`` c > 0: scores become c tanh(s / c)."""
     dt = _act(q, "q")
     assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype and out.is_contiguous()
     assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1)
     _check(_load().b2tts_sink_attn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), lay.tok_seq.data_ptr(),
                                    lay.positions.data_ptr(), lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(),
                                    lay.block_tables.data_ptr(), lay.block_tables.stride(0), _ptr(sink), _ptr(gate),
-                                   0 if gate is None else gate.stride(0), lay.n_tokens, lay.n_seqs, lay.max_new, heads, kv_heads, dim,
-                                   vdim, page, mask_kind, mask, scale, dt, path, _stream()), "sink_attn")
+                                   0 if gate is None else gate.stride(0), lay.n_tokens, lay.n_seqs, lay.max_new, heads, kv_heads,
+                                   kv_heads if v_heads is None else v_heads, dim, vdim, page, mask_kind, mask, keep_first, softcap,
+                                   scale, dt, path, _stream()), "sink_attn")
 
 
 def short_conv_act(u, c_off, channels, w, bias, state, lay, out, taps, act=1):
@@ -1024,6 +1042,70 @@ def delta_rule_scan(qkv, beta_in, a_in, a_log, dt_bias, state, out, lay, heads, 
                                          a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(), _coef(out, heads).data_ptr(),
                                          out.data_ptr(), *_seq_args(lay, True), heads, kv_heads, dim, vdim, dt, _stream()),
            "delta_rule_scan")
+
+
+def gated_linear_scan(q, k, v, z, z_bias, tau, state, out, lay, heads, dim, vdim):
+    """q, k [n, heads*dim], v [n, heads*vdim], z [n, heads*dim] (decay pre-activations): column slices with unit column
+    stride; decay = sigmoid(z + z_bias)^(1/tau) per key channel in float; state float [slots, heads, dim, vdim]; out float."""
+    _cuda(q, None, "q")
+    dt = DTYPE_CODE[q.dtype]
+    _cuda(state, F32, "state"); _cuda(out, F32, "out")
+    for t in (k, v, z):
+        assert t.dtype == q.dtype and t.stride(1) == 1
+    assert q.stride(1) == 1 and state.is_contiguous() and out.is_contiguous() and (z_bias is None or z_bias.dtype == F32)
+    decay = torch.empty(q.shape[0], heads * dim, dtype=F32, device=q.device)
+    _check(_load().b2tts_gated_linear_scan(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), z.data_ptr(),
+                                           z.stride(0), _ptr(z_bias), tau, decay.data_ptr(), state.data_ptr(), out.data_ptr(),
+                                           *_seq_args(lay, True), heads, dim, vdim, dt, _stream()), "gated_linear_scan")
+
+
+def sandwich_residual(x, g_out, *, a=None, a_index=None, b=None, wa=None, wb=None, branch_scale=1.0, z=None, zw=None, z_idx=None,
+                      n_real=0, hin=None, g_in=None, h_dtype=None, init=False, eps=1e-6, dtype=None):
+    """x (float [n, cols], in place; ``init``: starts from zero) += g_out * rms_norm(y); returns the next sublayer's input
+    g_in * rms_norm(x) in ``h_dtype`` when ``g_in`` is given.  y = a, or table row a[a_index], or branch_scale *
+    (rms_norm(a) * wa + rms_norm(b) * wb), plus sum_k zw[:, k] * (z_idx[:, k] < n_real ? z[:, k] : hin)."""
+    _cuda(x, F32, "x"); _cuda(g_out, F32, "g_out")
+    n, cols = x.shape
+    dtype = dtype or next(t.dtype for t in (a, z) if t is not None)
+    for t in (a, b, z, hin):
+        assert t is None or (t.dtype == dtype and t.is_contiguous())
+    for t in (wa, wb, zw, g_in):
+        assert t is None or (t.dtype == F32 and t.is_contiguous())
+    top = 0 if z is None else zw.shape[1]
+    h = torch.empty(n, cols, dtype=h_dtype or dtype, device=x.device) if g_in is not None else None
+    assert h is None or h.dtype == dtype
+    _check(_load().b2tts_sandwich_residual(x.data_ptr(), _ptr(a), _ptr(a_index), 0 if a_index is None else a.shape[0], _ptr(b), _ptr(wa),
+                                           _ptr(wb), branch_scale, _ptr(z), _ptr(zw), _ptr(z_idx), top, n_real, _ptr(hin),
+                                           g_out.data_ptr(), _ptr(g_in), _ptr(h), n, cols, int(init), eps, DTYPE_CODE[dtype], _stream()),
+           "sandwich_residual")
+    return h
+
+
+def polynorm_(y, coef, eps):
+    """In place on y [rows, cols]: coef[0] N(y) + coef[1] N(y^2) + coef[2] N(y^3) + coef[3], N = division by the row's root mean square."""
+    dt = _act(y, "y")
+    _cuda(coef, F32, "coef")
+    assert y.is_contiguous() and coef.numel() == 4
+    _check(_load().b2tts_polynorm(y.data_ptr(), coef.data_ptr(), y.numel() // y.shape[-1], y.shape[-1], eps, dt, _stream()), "polynorm")
+    return y
+
+
+def diff_combine(maps, out, lam, mult, heads, vdim, eps):
+    """maps [n, 2 * heads * vdim] (first map's heads, then the second's) -> out [n, heads * vdim] =
+    head_rms_norm(map1 - lam * map2) * mult."""
+    dt = _act(maps, "maps")
+    assert out.dtype == maps.dtype and maps.is_contiguous() and out.is_contiguous()
+    _check(_load().b2tts_diff_combine(maps.data_ptr(), out.data_ptr(), lam, mult, maps.shape[0], heads, vdim, eps, dt, _stream()),
+           "diff_combine")
+    return out
+
+
+def tanh_cap_(y, cap):
+    """In place on a float tensor: y <- cap * tanh(y / cap)."""
+    _cuda(y, F32, "y")
+    assert y.is_contiguous()
+    _check(_load().b2tts_tanh_cap(y.data_ptr(), y.numel(), cap, _stream()), "tanh_cap")
+    return y
 
 
 def matrix_memory_scan(q, k, v, ig, fg, i_bias, f_bias, cap, state, state_nm, gates, out, lay, heads, dim, vdim):

@@ -121,9 +121,12 @@ class FeedForwardSpec:
     experts: int = 0
     top: int = 0
     router_scale: float = 1.0
-    act: str = "relu2"             # "relu2": relu(up)^2;  "xielu": two learned numbers;  "silu_gate": silu(gate) * up
+    act: str = "relu2"             # "relu2": relu(up)^2;  "xielu": two learned numbers;  "silu_gate": silu(gate) * up;
+                                   # "polynorm": a N(z) + b N(z^2) + c N(z^3) + e with four learned numbers
     bias: bool = False             # dense projections carry biases
-    router: str = "sigmoid"        # "sigmoid": scores / their sum;  "softmax_chosen": logits + bias, softmax over the chosen
+    router: str = "sigmoid"        # "sigmoid": scores / their sum;  "softmax_chosen": logits + bias, softmax over the chosen;
+                                   # "softmax_all": softmax over all outputs, a correction enters the choice only
+    identity: int = 0              # router outputs beyond ``experts`` that stand for experts returning their input
 
 
 @dataclass
@@ -200,7 +203,8 @@ class BokenexConfig:
 @dataclass
 class RotarySpec:
     """Pair rotation of the first ``dims`` coordinates (2i with 2i+1) by position * base^(-2i/dims); ``scaling``
-    ({factor, original, fast, slow}) blends each frequency with its ``1/factor`` multiple over a ramp (YaRN)."""
+    {factor, original, fast, slow} blends each frequency with its ``1/factor`` multiple over a ramp (YaRN), ``scaling``
+    {factor} alone divides every frequency by it (linear)."""
     dims: int
     base: float
     scaling: dict | None = None
@@ -345,11 +349,14 @@ class SinkAttentionSpec:
     mask_kind: str                 # "window" | "chunk"
     mask_size: int
     scale: float
-    rot: HalfRotarySpec | None = None
+    rot: object | None = None      # HalfRotarySpec (i with i + dims/2) | RotarySpec (2i with 2i + 1)
     qk_norm: bool = False
     bias: bool = False
     gate: bool = False
     tied_values: bool = False
+    softcap: float = 0.0           # c > 0: scaled scores become c tanh(s / c)
+    keep_first: int = 0            # keys below this position stay visible behind the mask
+    sink: str = "learned"          # "learned": exp(sink_h) in the denominator;  "zero": exp(0);  "none": an ordinary softmax
 
 
 @dataclass
@@ -515,12 +522,169 @@ class TibivikConfig:
         return out
 
 
+@dataclass
+class DiffAttentionSpec:
+    """Differential attention: every head runs two softmax maps (their queries and keys stored side by side) over the
+    same values and returns map 1 - lambda * map 2, divided by its root mean square and multiplied by 1 - ``diff``.
+    ``window`` 0: causal; ``keep_first``: first keys that stay visible behind the window.  ``kv_from``: the layer has no
+    key/value projections and reads the cache of that (earlier) layer."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    diff: float
+    window: int = 0
+    keep_first: int = 0
+    kv_from: int | None = None
+
+
+@dataclass
+class GatedLinearSpec:
+    """Gated linear attention: a matrix state per head with one decay per key channel and token,
+    sigmoid(W_a2 W_a1 h + b)^(1/tau); ``decay_rank`` is the inner size of that two-step projection (0: not known yet,
+    read from the checkpoint's tensor shapes)."""
+    heads: int
+    dim: int
+    vdim: int
+    tau: float
+    decay_rank: int = 0
+
+
+@dataclass
+class TeberaxLayerSpec:
+    type: str                      # "attention" | "parallel" | "latent_attention"
+    mixer: object                  # DiffAttentionSpec | ParallelMixerSpec | LatentMixerSpec
+    mlp: FeedForwardSpec | None
+    raw: dict = field(default_factory=dict, repr=False)      # the layer's entry as read (kept for to_dict)
+
+
+@dataclass
+class TeberaxConfig:
+    """``config.json`` of a Teberax checkpoint: a decoder-only token model over one 32-bit residual stream whose
+    sublayers are normed on the way in and on the way out with single-gain RMS norms.  Layers are listed one by one with
+    their own sizes: differential window attention (optionally on another layer's keys and values), biased rotary
+    attention with a zero sink beside gated linear attention, or windowed latent attention; feed-forwards are dense with
+    PolyNorm, a softmax-routed mixture of SiLU-gated experts with identity experts, or absent.  Logits pass a tanh cap."""
+    architecture: str
+    vocab: int
+    width: int
+    norm_eps: float
+    logit_softcap: float
+    layers: list
+    max_positions = None           # positions enter through rotations only: no table bounds them
+
+    page_multiple = 16
+
+    @staticmethod
+    def _rot(r: dict | None):
+        if not r:
+            return None
+        sc = r.get("scaling")
+        return RotarySpec(int(r["dims"]), float(r["base"]), {"factor": float(sc["factor"])} if sc else None)
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "TeberaxConfig":
+        layers = []
+        for i, ld in enumerate(d["layers"]):
+            kind, m = ld["type"], ld["mixer"]
+            mask = m.get("mask") or {}
+            if kind == "attention":
+                src = m.get("kv_from")
+                mixer = DiffAttentionSpec(heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                          scale=float(m["scale"]), diff=float(m["diff"]), window=int(mask.get("size") or 0),
+                                          keep_first=int(mask.get("keep_first") or 0), kv_from=None if src is None else int(src))
+                if mixer.heads % mixer.kv_heads:
+                    raise ValueError(f"layer {i}: {mixer.heads} heads over {mixer.kv_heads} key/value heads")
+                if mixer.kv_from is not None:
+                    s = layers[mixer.kv_from].mixer if 0 <= mixer.kv_from < i else None
+                    if not isinstance(s, DiffAttentionSpec) or s.kv_from is not None or \
+                            (s.kv_heads, s.dim, s.vdim) != (mixer.kv_heads, mixer.dim, mixer.vdim):
+                        raise ValueError(f"layer {i}: kv_from {mixer.kv_from} must name an earlier attention layer with key/value "
+                                         "projections of its own and the same key/value sizes")
+            elif kind == "parallel":
+                lm, rt = m["left"], m["right"]
+                left = SinkAttentionSpec(heads=int(lm["heads"]), kv_heads=int(lm["kv_heads"]), dim=int(lm["dim"]), vdim=int(lm["vdim"]),
+                                         mask_kind="window", mask_size=0, scale=float(lm["scale"]), rot=cls._rot(lm.get("rot")),
+                                         bias=True, softcap=float(lm.get("softcap") or 0.0), sink="zero")
+                if left.heads % left.kv_heads:
+                    raise ValueError(f"layer {i}: {left.heads} heads over {left.kv_heads} key/value heads")
+                if left.rot is not None and (left.rot.dims % 2 or left.rot.dims > left.dim):
+                    raise ValueError(f"layer {i}: {left.rot.dims} rotated coordinates in a head of {left.dim}")
+                right = GatedLinearSpec(heads=int(rt["heads"]), dim=int(rt["dim"]), vdim=int(rt["vdim"]), tau=float(rt["tau"]),
+                                        decay_rank=int(rt.get("decay_rank") or 0))
+                mixer = ParallelMixerSpec(left, right, 0.5, 0.5)
+            elif kind == "latent_attention":
+                rot = cls._rot(m["rot"])
+                mixer = LatentMixerSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]), vdim=int(m["vdim"]),
+                                        kv_rank=int(m["kv_rank"]), q_rank=0, window=int(mask.get("size") or 0),
+                                        scale=float(m["scale"]), rot=rot, gate=False)
+                if rot.dims > mixer.rot_dim or rot.dims % 2:
+                    raise ValueError(f"layer {i}: {rot.dims} rotated dimensions in a part of {mixer.rot_dim}")
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            f = ld.get("mlp")
+            mlp = None
+            if f is not None:
+                if f["kind"] == "dense":
+                    mlp = FeedForwardSpec("dense", int(f["ff"]), act="polynorm")
+                elif f["kind"] == "moe":
+                    ro = f["router"]
+                    mlp = FeedForwardSpec("moe", int(f["expert"]["ff"]), int(ro["experts"]), int(ro["top"]), act="silu_gate",
+                                          router="softmax_all", identity=int(ro.get("identity") or 0))
+                    if not 1 <= mlp.top <= mlp.experts + mlp.identity:
+                        raise ValueError(f"layer {i}: top {mlp.top} of {mlp.experts} + {mlp.identity} experts")
+                else:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {f['kind']!r}")
+            layers.append(TeberaxLayerSpec(kind, mixer, mlp, raw=ld))
+        return cls(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]), norm_eps=float(d["norm"]["eps"]),
+                   logit_softcap=float(d.get("logit_softcap") or 0.0), layers=layers)
+
+    def complete_from_checkpoint(self, model_dir: str) -> None:
+        """Sizes that only a tensor's shape gives (the inner size of the decay projection) are read from the header of
+        ``model.safetensors``: 8 bytes of little-endian length, then that many bytes of JSON."""
+        todo = [i for i, l in enumerate(self.layers) if l.type == "parallel" and not l.mixer.right.decay_rank]
+        path = os.path.join(model_dir, "model.safetensors")
+        if not todo or not os.path.exists(path):
+            return
+        import struct
+        with open(path, "rb") as f:
+            (n,) = struct.unpack("<Q", f.read(8))
+            header = json.loads(f.read(n))
+        for i in todo:
+            self.layers[i].mixer.right.decay_rank = int(header[f"l{i}.mix.right.a1"]["shape"][0])
+
+    @classmethod
+    def from_pretrained(cls, model_dir: str) -> "TeberaxConfig":
+        with open(os.path.join(model_dir, "config.json")) as f:
+            c = cls.from_dict(json.load(f))
+        c.complete_from_checkpoint(model_dir)
+        return c
+
+    def to_dict(self) -> dict:
+        layers = []
+        for l in self.layers:
+            e = json.loads(json.dumps(l.raw))
+            if l.type == "parallel" and l.mixer.right.decay_rank:
+                e["mixer"]["right"]["decay_rank"] = l.mixer.right.decay_rank
+            layers.append(e)
+        out = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
+               "layers": layers}
+        if self.logit_softcap:
+            out["logit_softcap"] = self.logit_softcap
+        return out
+
+
 def load_model_config(model_dir: str):
-    """Parse ``config.json`` with the configuration class its architecture is registered under."""
+    """Parse ``config.json`` with the configuration class its architecture is registered under; a class that needs sizes
+    only the checkpoint's tensor shapes give completes itself from the file's header."""
     from .models.registry import resolve
     with open(os.path.join(model_dir, "config.json")) as f:
         d = json.load(f)
-    return resolve(d).config_cls.from_dict(d)
+    cfg = resolve(d).config_cls.from_dict(d)
+    if hasattr(cfg, "complete_from_checkpoint"):
+        cfg.complete_from_checkpoint(model_dir)
+    return cfg
 
 
 @dataclass

@@ -222,24 +222,25 @@ stream_gather_norm_kernel(const float* __restrict__ xs, const int32_t* __restric
 // One block per token.  q = u[q_off : +H*d] + q_bias, k = u[k_off : +G*d] + k_bias, v = u[v_off : +G*dv] + v_bias, or,
 // with v_off < 0, v = k as it stands here (before norm and rotation).  With norm weights, q and k are each divided by
 // the root mean square of their WHOLE projection and multiplied by the weight.  With rot_dims > 0, coordinate
-// i < rot_dims/2 of every head is paired with i + rot_dims/2 and the pair turned by position * freq[i].
+// i < rot_dims/2 of every head is paired with i + rot_dims/2 (or, `interleaved`, coordinate 2i with 2i + 1) and the pair
+// turned by position * freq[i].  Without caches (a layer that reads another layer's keys and values) only q is made.
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
 attn_prep_kernel(const T* __restrict__ u, int64_t ldu, int q_off, int k_off, int v_off, const float* __restrict__ q_bias,
                  const float* __restrict__ k_bias, const float* __restrict__ v_bias, const float* __restrict__ q_norm_w,
                  const float* __restrict__ k_norm_w, const float* __restrict__ freq, int rot_dims,
                  const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping, T* __restrict__ q_out,
-                 T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G, int d, int dv, float eps) {
+                 T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G, int Gv, int d, int dv, float eps, int interleaved) {
   __shared__ float red[33];
   const size_t t = blockIdx.x;
   const int slot = slot_mapping[t];
   if (slot < 0) return;                                   // padding row (uniform over the block)
   const T* ur = u + t * ldu;
-  const int nq = H * d, nk = G * d, nv = G * dv;
+  const int nq = H * d, nk = G * d, nv = Gv * dv;
   const float pos = static_cast<float>(positions[t]);
   // values
   T* vr = v_cache + static_cast<size_t>(slot) * nv;
-  for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+  for (int c = threadIdx.x; c < nv && v_cache != nullptr; c += blockDim.x) {
     float v;
     if (v_off >= 0) v = to_f(ur[v_off + c]) + (v_bias != nullptr ? v_bias[c] : 0.f);
     else v = to_f(ur[k_off + c]) + (k_bias != nullptr ? k_bias[c] : 0.f);
@@ -261,7 +262,7 @@ attn_prep_kernel(const T* __restrict__ u, int64_t ldu, int q_off, int k_off, int
   }
   const int half = rot_dims / 2;
   // a work item is one coordinate that passes unchanged, or one pair of rotated coordinates (owned by its first half)
-  for (int part = 0; part < 2; ++part) {
+  for (int part = 0; part < (k_cache != nullptr ? 2 : 1); ++part) {
     const int n = part == 0 ? nq : nk, off = part == 0 ? q_off : k_off;
     const float* bias = part == 0 ? q_bias : k_bias;
     const float* nw = part == 0 ? q_norm_w : k_norm_w;
@@ -269,15 +270,16 @@ attn_prep_kernel(const T* __restrict__ u, int64_t ldu, int q_off, int k_off, int
     T* dst = part == 0 ? q_out + t * nq : k_cache + static_cast<size_t>(slot) * nk;
     for (int c = threadIdx.x; c < n; c += blockDim.x) {
       const int i = c % d;
-      if (i >= half && i < rot_dims) continue;             // second half of a pair: written by its partner
+      const bool rotated = i < rot_dims;
+      if (rotated && (interleaved ? (i & 1) : i >= half)) continue;     // second of a pair: written by its partner
       float a = to_f(ur[off + c]) + (bias != nullptr ? bias[c] : 0.f);
       if (nw != nullptr) a = a * inv * nw[c];
-      if (i < half) {
-        const int c2 = c + half;
+      if (rotated) {
+        const int c2 = interleaved ? c + 1 : c + half;
         float b = to_f(ur[off + c2]) + (bias != nullptr ? bias[c2] : 0.f);
         if (nw != nullptr) b = b * inv * nw[c2];
         float sn, cs;
-        sincosf(pos * freq[i], &sn, &cs);
+        sincosf(pos * freq[interleaved ? i >> 1 : i], &sn, &cs);
         dst[c] = from_f<T>(a * cs - b * sn);
         dst[c2] = from_f<T>(b * cs + a * sn);
       } else {
@@ -646,25 +648,26 @@ extern "C" int b2tts_attn_prep(const void* u, int64_t ldu, int q_off, int k_off,
                                const float* k_bias, const float* v_bias, const float* q_norm_w, const float* k_norm_w,
                                const float* freq, int rot_dims, const int32_t* positions, const int32_t* slot_mapping,
                                void* q_out, void* k_cache, void* v_cache, int n_tokens, int heads, int kv_heads, int dim,
-                               int vdim, float eps, int dtype, void* stream) {
+                               int vdim, float eps, int interleaved, int v_heads, int dtype, void* stream) {
+  B2_REQUIRE(v_heads > 0 && (v_off >= 0 || v_heads == kv_heads), B2TTS_EINVAL, "attn_prep: %d value heads", v_heads);
   B2_REQUIRE(n_tokens >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && q_off >= 0 && k_off >= 0, B2TTS_EINVAL,
              "attn_prep: bad sizes");
+  B2_REQUIRE((k_cache == nullptr) == (v_cache == nullptr), B2TTS_EINVAL, "attn_prep: both caches, or neither");
   B2_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim, B2TTS_EINVAL, "attn_prep: %d rotated of %d coordinates", rot_dims, dim);
   B2_REQUIRE(v_off >= 0 || vdim == dim, B2TTS_EINVAL, "attn_prep: values that are the keys need vdim == dim");
   B2_REQUIRE((q_norm_w == nullptr) == (k_norm_w == nullptr), B2TTS_EINVAL, "attn_prep: norm weights for q and k, or neither");
   B2_REQUIRE(B2_ROW_DTYPE_OK(dtype), B2TTS_EINVAL, "attn_prep: dtype %d", dtype);
   if (n_tokens == 0) return B2TTS_OK;
-  B2_REQUIRE(u && positions && slot_mapping && q_out && k_cache && v_cache && (rot_dims == 0 || freq), B2TTS_EINVAL,
-             "attn_prep: null pointer");
+  B2_REQUIRE(u && positions && slot_mapping && q_out && (rot_dims == 0 || freq), B2TTS_EINVAL, "attn_prep: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == B2TTS_DTYPE_BF16)
     attn_prep_kernel<__nv_bfloat16><<<n_tokens, ROW_THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(u), ldu, q_off, k_off, v_off,
         q_bias, k_bias, v_bias, q_norm_w, k_norm_w, freq, rot_dims, positions, slot_mapping, static_cast<__nv_bfloat16*>(q_out),
-        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), heads, kv_heads, dim, vdim, eps);
+        static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), heads, kv_heads, v_heads, dim, vdim, eps, interleaved);
   else
     attn_prep_kernel<float><<<n_tokens, ROW_THREADS, 0, st>>>(static_cast<const float*>(u), ldu, q_off, k_off, v_off, q_bias, k_bias,
         v_bias, q_norm_w, k_norm_w, freq, rot_dims, positions, slot_mapping, static_cast<float*>(q_out),
-        static_cast<float*>(k_cache), static_cast<float*>(v_cache), heads, kv_heads, dim, vdim, eps);
+        static_cast<float*>(k_cache), static_cast<float*>(v_cache), heads, kv_heads, v_heads, dim, vdim, eps, interleaved);
   B2_CHECK_LAUNCH("attn_prep");
   return B2TTS_OK;
 }

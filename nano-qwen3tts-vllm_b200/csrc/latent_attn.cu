@@ -41,7 +41,7 @@ struct LatentAttnArgs {
   const void* qr; int64_t qr_tok, qr_head;      // un-rotated rotary query parts [.., dr]
   const void* cache;                            // [pages * page, r + dr]
   void* out; int64_t o_tok, o_head;             // weighted latent sums [.., r]
-  const float* sink;                            // [H]
+  const float* sink;                            // [H], or null: no sink, an ordinary softmax
   const float* freq; float rot_mult; int rot_dims;
   const int32_t *seq_start, *seq_pos0, *seq_len, *block_tables; int64_t bt_stride;
   int n_seqs, max_new, H, r, dr, page, window;
@@ -92,7 +92,8 @@ latent_attn_kernel(const LatentAttnArgs a) {
   const int32_t* bt = a.block_tables + b * a.bt_stride;
   const T* cache = static_cast<const T*>(a.cache);
   const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-  float m = a.sink[h], l = 1.0f;                 // the sink: exp(sink - m) with m = sink
+  float m = -1.0e30f, l = 0.f;
+  if (a.sink != nullptr) { m = a.sink[h]; l = 1.0f; }   // the sink: exp(sink - m) with m = sink; none: an ordinary softmax
   float o[LA_MAX_R_PER_LANE];
 #pragma unroll
   for (int i = 0; i < LA_MAX_R_PER_LANE; ++i) o[i] = 0.f;
@@ -276,8 +277,9 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
     const bool ok = tl < n_tok && h < a.H;
     row_pos[tid] = ok ? pos_first + tl : -1;
     // the sink counts once: the first split starts from it (m = sink, l = exp(sink - m) = 1), the others from nothing
-    row_m[tid] = ok && blockIdx.z == 0 ? a.sink[h] : -1.0e30f;
-    row_l[tid] = blockIdx.z == 0 ? 1.0f : 0.f;
+    const bool sunk = blockIdx.z == 0 && a.sink != nullptr;
+    row_m[tid] = ok && sunk ? a.sink[h] : -1.0e30f;
+    row_l[tid] = sunk ? 1.0f : 0.f;
   }
   {
     // a warp stages rows warp, warp + NW, ..: first every load of its rows is issued (16 bytes of ql per lane and step,
@@ -621,7 +623,7 @@ extern "C" int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head
   B2_REQUIRE(dtype == B2TTS_DTYPE_BF16 || dtype == B2TTS_DTYPE_F32, B2TTS_EINVAL, "latent_attn: dtype %d", dtype);
   B2_REQUIRE(kv_rank <= 32 * LA_MAX_R_PER_LANE, B2TTS_EUNSUPPORTED, "latent_attn: latent size %d > %d", kv_rank, 32 * LA_MAX_R_PER_LANE);
   if (n_seqs == 0 || max_new == 0) return B2TTS_OK;
-  B2_REQUIRE(ql && cache && out && sink && seq_start && seq_pos0 && seq_len && block_tables && (rot_dim == 0 || qr) &&
+  B2_REQUIRE(ql && cache && out && seq_start && seq_pos0 && seq_len && block_tables && (rot_dim == 0 || qr) &&
              (rot_dims == 0 || freq), B2TTS_EINVAL, "latent_attn: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   LatentAttnArgs a{ql, ql_tok, ql_head, qr, qr_tok, qr_head, cache, out, o_tok, o_head, sink, freq, rot_mult, rot_dims,

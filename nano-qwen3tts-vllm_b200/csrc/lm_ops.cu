@@ -414,9 +414,12 @@ __global__ void conv_state_update_kernel(const T* __restrict__ u, int64_t u_stri
   }
 }
 
-// ------------------------------------------------------------------ sigmoid top-k router
-// One warp per token: logits over the experts in 32-bit, scores = sigmoid, the `top` largest (ties: the lower index),
-// weights = score / (sum of the chosen scores + 1e-20) * scale.
+// ------------------------------------------------------------------ top-k router
+// One warp per token: logits over the experts in 32-bit, the `top` largest scores chosen (ties: the lower index).
+// mode 0: scores = sigmoid, weights = score / (sum of the chosen scores + 1e-20) * scale.
+// mode 1: scores = logits + bias, weights = softmax over the chosen scores * scale.
+// mode 2: scores = softmax over ALL logits; the choice is made on score + bias, the weights are the chosen scores
+//         themselves * scale, not renormalised.
 constexpr int ROUTE_WARPS = 4;
 constexpr int ROUTE_MAX_EXPERTS = 256;
 
@@ -424,8 +427,10 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E, cols] */, int32_t* __restrict__ top_idx,
                  float* __restrict__ top_w, int n_tokens, int cols, int E, int top, float scale,
-                 const float* __restrict__ bias /* [E] or null */, int softmax_chosen) {
+                 const float* __restrict__ bias /* [E] or null */, int mode) {
   __shared__ float score[ROUTE_WARPS][ROUTE_MAX_EXPERTS];
+  __shared__ float weight[ROUTE_WARPS][ROUTE_MAX_EXPERTS];   // mode 2: the scores the weights are taken from
+  const int softmax_chosen = mode == 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n = blockIdx.x * ROUTE_WARPS + warp;
   if (n >= n_tokens) return;
@@ -436,7 +441,9 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E
     for (int c = lane; c < cols; c += 32) acc += to_f(hr[c]) * wr[c];
     acc = warp_sum(acc);
     if (lane == 0) {
-      if (softmax_chosen) {
+      if (mode == 2) {
+        score[warp][e] = acc >= -3.0e38f ? acc : -3.0e38f;
+      } else if (softmax_chosen) {
         const float sc = acc + (bias != nullptr ? bias[e] : 0.f);
         score[warp][e] = sc >= -3.0e38f ? sc : -3.0e38f;  // a NaN input still yields valid expert ids
       } else {
@@ -446,6 +453,20 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E
     }
   }
   __syncwarp();
+  if (mode == 2) {                                       // softmax over all experts, then the choice scores
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, score[warp][e]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) den += expf(score[warp][e] - mx);
+    den = warp_sum(den);
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(score[warp][e] - mx) / den;
+      weight[warp][e] = p;
+      score[warp][e] = p + (bias != nullptr ? bias[e] : 0.f);
+    }
+    __syncwarp();
+  }
   float sum = 0.f, first = 0.f;
   float chosen_s = 0.f;          // lane k keeps the k-th choice
   int chosen_e = 0;
@@ -464,6 +485,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E
     }
     if (k == 0) first = best;
     if (softmax_chosen) best = expf(best - first);       // weights: the softmax over the chosen logits only
+    if (mode == 2) best = weight[warp][be];
     if (lane == (k & 31)) { chosen_s = best; chosen_e = be; }
     sum += best;
     if (lane == 0) score[warp][be] = -INFINITY;
@@ -471,7 +493,8 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E
   }
   if (lane < top) {
     top_idx[static_cast<size_t>(n) * top + lane] = chosen_e;
-    top_w[static_cast<size_t>(n) * top + lane] = softmax_chosen ? chosen_s / sum * scale : chosen_s / (sum + 1e-20f) * scale;
+    top_w[static_cast<size_t>(n) * top + lane] = mode == 2 ? chosen_s * scale
+                                                 : softmax_chosen ? chosen_s / sum * scale : chosen_s / (sum + 1e-20f) * scale;
   }
 }
 
@@ -632,9 +655,10 @@ extern "C" int b2tts_conv_headnorm_kvwrite(const void* u, int64_t u_stride, cons
 
 extern "C" int b2tts_moe_route(const void* h, const float* router, int32_t* top_idx, float* top_w, int32_t* offsets,
                                int32_t* sorted_pair, int n_tokens, int cols, int experts, int top, float scale,
-                               const float* bias, int softmax_chosen, int dtype, void* stream) {
+                               const float* bias, int mode, int dtype, void* stream) {
   using namespace b2;
   B2_REQUIRE(n_tokens >= 0 && cols > 0 && experts > 0 && top > 0 && top <= experts, B2TTS_EINVAL, "moe_route: bad sizes");
+  B2_REQUIRE(mode >= 0 && mode <= 2, B2TTS_EINVAL, "moe_route: mode %d", mode);
   B2_REQUIRE(experts <= ROUTE_MAX_EXPERTS && top <= 32, B2TTS_EUNSUPPORTED, "moe_route: experts %d > %d or top %d > 32", experts,
              ROUTE_MAX_EXPERTS, top);
   B2_REQUIRE(LM_DTYPE_OK(dtype), B2TTS_EINVAL, "moe_route: dtype %d", dtype);
@@ -645,10 +669,10 @@ extern "C" int b2tts_moe_route(const void* h, const float* router, int32_t* top_
     const int grid = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
     if (dtype == B2TTS_DTYPE_BF16)
       moe_route_kernel<__nv_bfloat16><<<grid, ROUTE_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(h), router, top_idx, top_w,
-                                                                          n_tokens, cols, experts, top, scale, bias, softmax_chosen);
+                                                                          n_tokens, cols, experts, top, scale, bias, mode);
     else
       moe_route_kernel<float><<<grid, ROUTE_WARPS * 32, 0, st>>>(static_cast<const float*>(h), router, top_idx, top_w, n_tokens, cols,
-                                                                 experts, top, scale, bias, softmax_chosen);
+                                                                 experts, top, scale, bias, mode);
     B2_CHECK_LAUNCH("moe_route");
   }
   moe_group_kernel<<<1, 1024, 0, st>>>(top_idx, offsets, sorted_pair, n_tokens * top, experts);

@@ -4,6 +4,7 @@
 //   matrix memory    S <- a S + b k v^T,  n <- a n + b k                   o = S^T q / (max(|n.q|, exp(-m)) + 1e-6)
 //                    with log gates i, f and the running maximum m = max(f + m, i), a = exp(f + m_old - m), b = exp(i - m)
 //   delta rule       S <- g S;  u = beta (v - S^T k);  S <- S + k u^T      o = S^T q
+//   gated linear     S <- diag(alpha) S + k v^T                            o = S^T q      (a decay per key channel and token)
 //
 // All three update every value column of S independently.  A column is shared by RS = ceil(key size / 32) lanes of one
 // warp, each keeping 32 rows of it in registers for the whole portion; sums over the rows (the read-out, the delta rule's
@@ -29,13 +30,14 @@ constexpr int SCAN_COLS = 32;             // value columns per CTA
 constexpr int SCAN_PER = 8;               // key elements per lane of the one-warp gate kernel: key sizes up to 256
 constexpr int SCAN_DEPTH = 4;             // tokens whose inputs are in flight in registers
 
-enum { SCAN_LINEAR = 0, SCAN_DELTA = 1 };
+enum { SCAN_LINEAR = 0, SCAN_DELTA = 1, SCAN_GATED = 2 };
 
 struct ScanArgs {
   const void* k; int64_t ldk;             // key-like vectors: (row, group g, i) at k[row * ldk + g * d + i]
   const void* q; int64_t ldq;             // query-like vectors, same layout
   const void* v; int64_t ldv;             // values: (row, head h, c) at v[row * ldv + h * dv + c]
-  const float* coef;                      // [rows, H, 3] per-token scalars, see scan_kernel
+  const float* coef;                      // [rows, H, 3] per-token scalars, see scan_kernel (SCAN_GATED: unused)
+  const float* decay; int64_t ldd;        // SCAN_GATED: per key channel, (row, head h, i) at decay[row * ldd + h * d + i]
   const float* skip;                      // [H] or null: out += skip[h] * value
   float* state;                           // [slots, H, d, dv]
   float* out;                             // [rows, H * dv]
@@ -56,6 +58,7 @@ __device__ __forceinline__ float slice_sum(float v) {
 // Per-token scalars c = coef[row, h, :], computed beforehand (they depend on the inputs only, not on the state):
 //   SCAN_LINEAR   S <- c0 S + k (c1 v)^T;                               out = S^T q * qscale [/ c2] [+ skip v]
 //   SCAN_DELTA    S <- c0 S; u = c1 (v - S^T k^); S <- S + k^ u^T;      out = S^T q^ * qscale      (k^, q^: unit vectors)
+//   SCAN_GATED    S[i, :] <- decay[i] S[i, :] + k[i] v^T;               out = S^T q * qscale       (decay staged like k and q)
 // RS = threads per value column = ceil(d / 32) rounded up to a power of two; the CTA is RS warps and owns 32 columns.  A
 // warp holds 32 / RS columns; thread (slice, column) keeps rows slice * 32 .. + 31 of its column in registers for the
 // whole portion.  Thread i stages element i of a token's k and q (zero beyond d) in shared memory, SCAN_DEPTH tokens at a
@@ -65,7 +68,8 @@ __global__ void __launch_bounds__(32 * RS)
 scan_kernel(const ScanArgs a) {
   constexpr int CW = 32 / RS;                              // columns per warp
   constexpr int DP = RS * SCAN_ROWS;                       // padded key size = threads
-  __shared__ __align__(16) float vec[2][SCAN_DEPTH][2][DP];   // [buffer][token of the group][k | q][row]
+  constexpr int NV = KIND == SCAN_GATED ? 3 : 2;
+  __shared__ __align__(16) float vec[2][SCAN_DEPTH][NV][DP];  // [buffer][token of the group][k | q | decay][row]
   const int b = blockIdx.z, h = blockIdx.y;
   const int len = a.seq_len[b];
   if (len <= 0) return;
@@ -88,21 +92,27 @@ scan_kernel(const ScanArgs a) {
   const T* qp = static_cast<const T*>(a.q) + static_cast<size_t>(start) * a.ldq + g * d + tid;
   const T* vp = static_cast<const T*>(a.v) + static_cast<size_t>(start) * a.ldv + h * dv + col;
   const float* cp = a.coef + (static_cast<size_t>(start) * H + h) * 3;
+  const float* dp = KIND == SCAN_GATED ? a.decay + static_cast<size_t>(start) * a.ldd + h * d + tid : nullptr;
   float* op = a.out + static_cast<size_t>(start) * H * dv + h * dv + col;
   const float skip = a.skip != nullptr ? a.skip[h] : 0.f;
 
   // the loaded values stay as they came (type T) until their token is staged: converting them at once would make the
   // thread wait for the load, four tokens early
   T rk[SCAN_DEPTH], rq[SCAN_DEPTH], rv[SCAN_DEPTH];
-  float rc[SCAN_DEPTH][3];
+  float rc[SCAN_DEPTH][3], rd[SCAN_DEPTH];
   auto fetch = [&](int u, int t) {                         // token t's inputs into register stage u
     rk[u] = rq[u] = rv[u] = from_f<T>(0.f);
     rc[u][0] = rc[u][1] = 0.f; rc[u][2] = 1.f;
+    rd[u] = 0.f;
     if (t < len) {
       if (mine) { rk[u] = kp[static_cast<size_t>(t) * a.ldk]; rq[u] = qp[static_cast<size_t>(t) * a.ldq]; }
       if (live) rv[u] = vp[static_cast<size_t>(t) * a.ldv];
-      const float* c = cp + static_cast<size_t>(t) * H * 3;
-      rc[u][0] = c[0]; rc[u][1] = c[1]; rc[u][2] = c[2];
+      if constexpr (KIND == SCAN_GATED) {
+        if (mine) rd[u] = dp[static_cast<size_t>(t) * a.ldd];
+      } else {
+        const float* c = cp + static_cast<size_t>(t) * H * 3;
+        rc[u][0] = c[0]; rc[u][1] = c[1]; rc[u][2] = c[2];
+      }
     }
   };
 #pragma unroll
@@ -115,6 +125,7 @@ scan_kernel(const ScanArgs a) {
     for (int u = 0; u < SCAN_DEPTH; ++u) {
       vec[grp][u][0][tid] = to_f(rk[u]);
       vec[grp][u][1][tid] = to_f(rq[u]);
+      if constexpr (KIND == SCAN_GATED) vec[grp][u][2][tid] = rd[u];
       vals[u] = to_f(rv[u]);
       cs[u][0] = rc[u][0]; cs[u][1] = rc[u][1]; cs[u][2] = rc[u][2];
     }
@@ -148,6 +159,19 @@ scan_kernel(const ScanArgs a) {
         o = slice_sum<RS>((o0 + o1) + (o2 + o3)) * a.qscale;
         if (a.divide) o /= c2;
         o += skip * val;
+      } else if constexpr (KIND == SCAN_GATED) {
+        const float* as = vec[grp][u][2];
+#pragma unroll
+        for (int x = 0; x < SCAN_ROWS; x += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qs + r0 + x);
+          const float4 a4 = *reinterpret_cast<const float4*>(as + r0 + x);
+          S[x] = a4.x * S[x] + kr[x] * val;             o0 += S[x] * q4.x;
+          S[x + 1] = a4.y * S[x + 1] + kr[x + 1] * val; o1 += S[x + 1] * q4.y;
+          S[x + 2] = a4.z * S[x + 2] + kr[x + 2] * val; o2 += S[x + 2] * q4.z;
+          S[x + 3] = a4.w * S[x + 3] + kr[x + 3] * val; o3 += S[x + 3] * q4.w;
+        }
+        o = slice_sum<RS>((o0 + o1) + (o2 + o3)) * a.qscale;
+        (void)c0; (void)c1; (void)c2;
       } else {
         // unit vectors: every thread sums the squares of its slice, the slices of a column add up to the whole vector
         float ssk = 0.f, ssq = 0.f, kv0 = 0.f, kv1 = 0.f;
@@ -270,6 +294,17 @@ matrix_memory_gates_kernel(const T* __restrict__ k, const T* __restrict__ q, int
     if (i < d) nm[i] = n[x];
   }
   if (lane == 0) nm[d] = m;
+}
+
+// decay of the gated linear recurrence: alpha = sigmoid(z + bias)^(1 / tau) = exp(logsigmoid(z + bias) / tau), in float
+template <typename T>
+__global__ void gated_decay_kernel(const T* __restrict__ z, int64_t ldz, const float* __restrict__ bias, float inv_tau,
+                                   float* __restrict__ decay, int n_tokens, int cols) {
+  const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<size_t>(n_tokens) * cols) return;
+  const size_t t = idx / cols;
+  const int c = static_cast<int>(idx % cols);
+  decay[idx] = expf(logsigmoid_f(to_f(z[t * ldz + c]) + (bias != nullptr ? bias[c] : 0.f)) * inv_tau);
 }
 
 template <typename T, int KIND, int RS>
@@ -405,5 +440,35 @@ extern "C" int b2tts_matrix_memory_scan(const void* q, const void* k, const void
                                            : launch_scan<float, SCAN_LINEAR>(a, n_seqs, st, "matrix_memory_scan");
   if (rc != B2TTS_OK) return rc;
   B2_CHECK_LAUNCH("matrix_memory_scan");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_gated_linear_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, const void* z,
+                                       int64_t ldz, const float* z_bias, float tau, float* decay, float* state, float* out,
+                                       const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
+                                       const int32_t* seq_slot, int n_tokens, int n_seqs, int heads, int dim, int vdim, int dtype,
+                                       void* stream) {
+  SCAN_COMMON_CHECKS("gated_linear_scan");
+  if (n_tokens <= 0) return B2TTS_OK;
+  B2_REQUIRE(q && k && v && z && decay && tau > 0.f, B2TTS_EINVAL, "gated_linear_scan: null pointer or tau <= 0");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int cols = heads * dim;
+  const size_t total = static_cast<size_t>(n_tokens) * cols;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  if (dtype == B2TTS_DTYPE_BF16)
+    gated_decay_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(z), ldz, z_bias, 1.0f / tau, decay, n_tokens, cols);
+  else
+    gated_decay_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(z), ldz, z_bias, 1.0f / tau, decay, n_tokens, cols);
+  B2_CHECK_LAUNCH("gated_linear_scan (decays)");
+  ScanArgs a{};
+  a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv;
+  a.decay = decay; a.ldd = cols;
+  a.state = state; a.out = out;
+  a.seq_start = seq_start; a.seq_pos0 = seq_pos0; a.seq_len = seq_len; a.seq_slot = seq_slot;
+  a.H = heads; a.G = heads; a.d = dim; a.dv = vdim; a.qscale = 1.0f / sqrtf(static_cast<float>(dim)); a.divide = 0;
+  const int rc = dtype == B2TTS_DTYPE_BF16 ? launch_scan<__nv_bfloat16, SCAN_GATED>(a, n_seqs, st, "gated_linear_scan")
+                                           : launch_scan<float, SCAN_GATED>(a, n_seqs, st, "gated_linear_scan");
+  if (rc != B2TTS_OK) return rc;
+  B2_CHECK_LAUNCH("gated_linear_scan");
   return B2TTS_OK;
 }

@@ -1,0 +1,231 @@
+// sandwich_ops.cu - per-row kernels of decoders whose sublayers are normed on the way in AND on the way out, both with a
+// single-gain RMS norm ("sandwich" layers over a 32-bit residual stream):
+//
+//   x <- x + g_out N(y),   h = g_in N(x)          N(v) = v / sqrt(mean(v^2) + eps),  g_out / g_in one number each
+//
+// One launch does the residual update of a finished sublayer and the input norm of the next one.  What y is made of is
+// chosen by the arguments:
+//   a dense output                        y = a
+//   an embedding row                      y = table[index[r]], and x starts from zero
+//   two branches of a parallel mixer      y = c (N(a) * wa + N(b) * wb), each branch normed over the row with its weight vector
+//   a mixture of experts                  y = sum_k zw[r, k] * (idx[r, k] < n_real ? z[r * top + k] : hin[r])
+//                                         (choices >= n_real are identity experts: they return the sublayer's input)
+// plus the small per-row pieces the same models need: PolyNorm, the combination of two attention maps that share their
+// values (differential attention), and a tanh cap on logits.
+//
+// Activations are `T` = bf16 (serving) or float (the all-32-bit mode); the stream, every sum of squares and every norm
+// are float in both.  Nothing allocates or synchronises; every launch is graph-capturable.
+#include <algorithm>
+
+#include "row_ops.cuh"
+
+namespace b2 {
+namespace row {
+
+constexpr int SW_THREADS = 256;
+
+struct SandwichArgs {
+  float* x;                       // [rows, cols] the stream, updated in place
+  const void* a;                  // [*, cols] dense output, first branch, or the embedding table
+  const int32_t* a_index;         // row of `a` for stream row r (null: r)
+  int a_rows;                     // rows of `a` when indexed (ids outside read as row 0)
+  const void* b;                  // second branch (with wa, wb)
+  const float* wa; const float* wb; float branch_scale;
+  const void* z; const float* zw; const int32_t* z_idx; int top, n_real;
+  const void* hin;                // the sublayer's input (identity experts)
+  const float* g_out;             // [1]
+  const float* g_in;              // [1] (with h)
+  void* h;                        // [rows, cols] the next sublayer's input, or null
+  int cols, init;
+  float eps;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(SW_THREADS)
+sandwich_residual_kernel(const SandwichArgs p) {
+  extern __shared__ float ybuf[];                       // [cols]
+  __shared__ float red[33];
+  const size_t r = blockIdx.x;
+  const int cols = p.cols;
+  const float fc = static_cast<float>(cols);
+  const T* a = static_cast<const T*>(p.a);
+  if (a != nullptr) {
+    size_t ar = r;
+    if (p.a_index != nullptr) {
+      const int id = p.a_index[r];
+      ar = (id >= 0 && id < p.a_rows) ? id : 0;
+    }
+    a += ar * cols;
+  }
+  float ssq = 0.f;
+  if (p.wa != nullptr) {                                // two branches, each normed with its own weight vector
+    const T* b = static_cast<const T*>(p.b) + r * cols;
+    float sa = 0.f, sb = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float va = to_f(a[c]), vb = to_f(b[c]);
+      sa += va * va; sb += vb * vb;
+    }
+    const float ia = 1.0f / sqrtf(block_sum(sa, red) / fc + p.eps);
+    const float ib = 1.0f / sqrtf(block_sum(sb, red) / fc + p.eps);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      const float y = p.branch_scale * (to_f(a[c]) * ia * p.wa[c] + to_f(b[c]) * ib * p.wb[c]);
+      ybuf[c] = y;
+      ssq += y * y;
+    }
+  } else {
+    const T* z = static_cast<const T*>(p.z);
+    const T* hin = p.hin != nullptr ? static_cast<const T*>(p.hin) + r * cols : nullptr;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      float y = a != nullptr ? to_f(a[c]) : 0.f;
+      for (int k = 0; k < p.top; ++k) {                 // choices in ascending order: a fixed order of additions
+        const size_t pr = r * p.top + k;
+        const bool real = p.z_idx == nullptr || p.z_idx[pr] < p.n_real;
+        y += p.zw[pr] * (real ? to_f(z[pr * cols + c]) : to_f(hin[c]));
+      }
+      ybuf[c] = y;
+      ssq += y * y;
+    }
+  }
+  const float inv = p.g_out[0] / sqrtf(block_sum(ssq, red) / fc + p.eps);
+  float* xr = p.x + r * cols;
+  float sx = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = (p.init ? 0.f : xr[c]) + ybuf[c] * inv;
+    xr[c] = v;
+    ybuf[c] = v;
+    sx += v * v;
+  }
+  if (p.h == nullptr) return;
+  const float inv2 = p.g_in[0] / sqrtf(block_sum(sx, red) / fc + p.eps);
+  T* hr = static_cast<T*>(p.h) + r * cols;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) hr[c] = from_f<T>(ybuf[c] * inv2);
+}
+
+// ------------------------------------------------------------------ PolyNorm, in place on the rows of y [rows, cols]
+// y <- c0 N(y) + c1 N(y^2) + c2 N(y^3) + c3, powers element by element, N over the row.
+template <typename T>
+__global__ void __launch_bounds__(SW_THREADS)
+polynorm_kernel(T* __restrict__ y, const float* __restrict__ coef, int cols, float eps) {
+  __shared__ float red[33];
+  T* yr = y + static_cast<size_t>(blockIdx.x) * cols;
+  float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = to_f(yr[c]), v2 = v * v;
+    s2 += v2; s4 += v2 * v2; s6 += v2 * v2 * v2;
+  }
+  const float fc = static_cast<float>(cols);
+  const float i1 = coef[0] / sqrtf(block_sum(s2, red) / fc + eps);
+  const float i2 = coef[1] / sqrtf(block_sum(s4, red) / fc + eps);
+  const float i3 = coef[2] / sqrtf(block_sum(s6, red) / fc + eps);
+  const float c3 = coef[3];
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = to_f(yr[c]), v2 = v * v;
+    yr[c] = from_f<T>(v * i1 + v2 * i2 + v2 * v * i3 + c3);
+  }
+}
+
+// ------------------------------------------------------------------ two attention maps over the same values -> one output
+// maps [rows, 2, H, dv] (the first map's heads, then the second map's); out[r, h] = N_head(maps[r, 0, h] - lambda * maps[r, 1, h])
+// * mult, N over the head's dv values without a weight.  One warp per (row, head).
+constexpr int DC_PER_LANE = 8;                          // value sizes up to 256
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const T* __restrict__ maps, T* __restrict__ out, float lambda, float mult, int rows, int H, int dv, float eps) {
+  const int lane = threadIdx.x & 31;
+  const size_t w = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= static_cast<size_t>(rows) * H) return;
+  const size_t r = w / H;
+  const int h = static_cast<int>(w % H);
+  const T* m1 = maps + (r * 2 * H + h) * dv;
+  const T* m2 = m1 + static_cast<size_t>(H) * dv;
+  float o[DC_PER_LANE], ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < DC_PER_LANE; ++i) {
+    const int c = i * 32 + lane;
+    o[i] = c < dv ? to_f(m1[c]) - lambda * to_f(m2[c]) : 0.f;
+    ss += o[i] * o[i];
+  }
+  const float inv = mult / sqrtf(warp_sum(ss) / static_cast<float>(dv) + eps);
+  T* orow = out + (r * H + h) * dv;
+#pragma unroll
+  for (int i = 0; i < DC_PER_LANE; ++i) {
+    const int c = i * 32 + lane;
+    if (c < dv) orow[c] = from_f<T>(o[i] * inv);
+  }
+}
+
+__global__ void tanh_cap_kernel(float* __restrict__ y, size_t n, float cap) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = cap * tanhf(y[i] / cap);
+}
+
+}  // namespace row
+}  // namespace b2
+
+using namespace b2;
+using namespace b2::row;
+
+extern "C" int b2tts_sandwich_residual(float* x, const void* a, const int32_t* a_index, int a_rows, const void* b, const float* wa,
+                                       const float* wb, float branch_scale, const void* z, const float* zw, const int32_t* z_idx,
+                                       int top, int n_real, const void* hin, const float* g_out, const float* g_in, void* h,
+                                       int rows, int cols, int init, float eps, int dtype, void* stream) {
+  B2_REQUIRE(rows >= 0 && cols > 0 && top >= 0, B2TTS_EINVAL, "sandwich_residual: rows=%d cols=%d top=%d", rows, cols, top);
+  B2_REQUIRE(B2_ROW_DTYPE_OK(dtype), B2TTS_EINVAL, "sandwich_residual: dtype %d", dtype);
+  B2_REQUIRE(cols <= 12 * 1024, B2TTS_EUNSUPPORTED, "sandwich_residual: %d columns above %d", cols, 12 * 1024);
+  if (rows == 0) return B2TTS_OK;
+  B2_REQUIRE(x && g_out && (!h || g_in), B2TTS_EINVAL, "sandwich_residual: null pointer");
+  B2_REQUIRE((wa == nullptr) == (wb == nullptr) && (wa == nullptr || (a && b && top == 0)), B2TTS_EINVAL,
+             "sandwich_residual: two branches need a, b and both weight vectors, and no experts");
+  B2_REQUIRE(top == 0 || (z && zw && (z_idx == nullptr || hin)), B2TTS_EINVAL, "sandwich_residual: experts need z, zw (and hin with z_idx)");
+  B2_REQUIRE(a || top > 0, B2TTS_EINVAL, "sandwich_residual: nothing to add");
+  B2_REQUIRE(a_index == nullptr || (a && a_rows > 0), B2TTS_EINVAL, "sandwich_residual: indexed rows need a table");
+  SandwichArgs p{x, a, a_index, a_rows, b, wa, wb, branch_scale, z, zw, z_idx, top, n_real, hin, g_out, g_in, h, cols, init, eps};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t sm = static_cast<size_t>(cols) * sizeof(float);
+  if (dtype == B2TTS_DTYPE_BF16) sandwich_residual_kernel<__nv_bfloat16><<<rows, SW_THREADS, sm, st>>>(p);
+  else sandwich_residual_kernel<float><<<rows, SW_THREADS, sm, st>>>(p);
+  B2_CHECK_LAUNCH("sandwich_residual");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_polynorm(void* y, const float* coef, int rows, int cols, float eps, int dtype, void* stream) {
+  B2_REQUIRE(rows >= 0 && cols > 0, B2TTS_EINVAL, "polynorm: rows=%d cols=%d", rows, cols);
+  B2_REQUIRE(B2_ROW_DTYPE_OK(dtype), B2TTS_EINVAL, "polynorm: dtype %d", dtype);
+  if (rows == 0) return B2TTS_OK;
+  B2_REQUIRE(y && coef, B2TTS_EINVAL, "polynorm: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B2TTS_DTYPE_BF16) polynorm_kernel<__nv_bfloat16><<<rows, SW_THREADS, 0, st>>>(static_cast<__nv_bfloat16*>(y), coef, cols, eps);
+  else polynorm_kernel<float><<<rows, SW_THREADS, 0, st>>>(static_cast<float*>(y), coef, cols, eps);
+  B2_CHECK_LAUNCH("polynorm");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_diff_combine(const void* maps, void* out, float lambda, float mult, int rows, int heads, int vdim, float eps,
+                                  int dtype, void* stream) {
+  B2_REQUIRE(rows >= 0 && heads > 0 && vdim > 0, B2TTS_EINVAL, "diff_combine: rows=%d heads=%d vdim=%d", rows, heads, vdim);
+  B2_REQUIRE(vdim <= 32 * DC_PER_LANE, B2TTS_EUNSUPPORTED, "diff_combine: value size %d above %d", vdim, 32 * DC_PER_LANE);
+  B2_REQUIRE(B2_ROW_DTYPE_OK(dtype), B2TTS_EINVAL, "diff_combine: dtype %d", dtype);
+  if (rows == 0) return B2TTS_OK;
+  B2_REQUIRE(maps && out, B2TTS_EINVAL, "diff_combine: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t warps = static_cast<size_t>(rows) * heads;
+  const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
+  if (dtype == B2TTS_DTYPE_BF16)
+    diff_combine_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(maps), static_cast<__nv_bfloat16*>(out),
+                                                               lambda, mult, rows, heads, vdim, eps);
+  else
+    diff_combine_kernel<float><<<blocks, 128, 0, st>>>(static_cast<const float*>(maps), static_cast<float*>(out), lambda, mult, rows, heads,
+                                                       vdim, eps);
+  B2_CHECK_LAUNCH("diff_combine");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_tanh_cap(float* y, int64_t n, float cap, void* stream) {
+  B2_REQUIRE(n >= 0 && cap > 0.f, B2TTS_EINVAL, "tanh_cap: n=%lld cap=%g", static_cast<long long>(n), cap);
+  if (n == 0) return B2TTS_OK;
+  B2_REQUIRE(y, B2TTS_EINVAL, "tanh_cap: null pointer");
+  tanh_cap_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(y, static_cast<size_t>(n), cap);
+  B2_CHECK_LAUNCH("tanh_cap");
+  return B2TTS_OK;
+}

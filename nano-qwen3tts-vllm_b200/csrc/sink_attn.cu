@@ -7,6 +7,11 @@
 // Both masks are a lower bound on j, so one kernel serves them.  The sink has no key and no value and is not scaled.  An
 // optional per-head gate multiplies the head's output by sigmoid(gate[t, h]).
 //
+// Three more switches, each off at its neutral value: keep_first F > 0 lets every token also see the keys j < F that its mask
+// hides (the kernels then walk a virtual key list, [0, min(F, lo)) followed by [lo, i]); softcap c > 0 turns a scaled score
+// s into c tanh(s / c) before the softmax; v_heads < kv_heads makes key head g read value head g mod v_heads (several key
+// maps over one set of values).
+//
 // Three kernels share a launch: prompt portions in bf16 with head sizes 32..128 x 64, 128 run on the tensor cores
 // (sink_attn_mma_kernel), rows with ONE new token and a head size of 4, 8, 16 or 32 16-byte pieces (d = dv) in a kernel whose
 // lanes split a cached row (sink_attn_decode_kernel), everything else in the plain kernel; each skips the rows of the others.
@@ -105,8 +110,8 @@ __global__ void __launch_bounds__(SA_WARPS * 32)
 sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_len,
                  const int32_t* __restrict__ block_tables, int64_t bt_stride, const float* __restrict__ sink,
-                 const T* __restrict__ gate, int64_t ldg, int H, int G, int d, int dv, int page, int mask_kind, int mask,
-                 float scale, int only_single) {
+                 const T* __restrict__ gate, int64_t ldg, int H, int G, int Gv, int d, int dv, int page, int mask_kind, int mask,
+                 int keep_first, float softcap, float scale, int only_single) {
   extern __shared__ float smem[];
   const int qstride = (d + 3) & ~3;
   float* qs = smem;                                   // [REP][qstride]
@@ -129,7 +134,8 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
   for (int c = threadIdx.x; c < REP * d; c += blockDim.x) qs[(c / d) * qstride + c % d] = to_f(qr[c]);
   __syncthreads();
   const int32_t* bt = block_tables + static_cast<int64_t>(b) * bt_stride;
-  const int nk = G * d, nv = G * dv;
+  const int nk = G * d, nv = Gv * dv, gv = g % Gv;
+  const int npre = min(keep_first, lo);                // kept first keys the mask hides: they come first in the key list
   const bool vec = (d % Vec16<T>::N) == 0;            // rows then start on 16-byte boundaries (the cache base is aligned)
   // a lane owns `cpl` consecutive value columns; with dv a multiple of 32 they are one aligned vector load per key
   const int cpl = (dv + 31) / 32, c_lane = lane * cpl;
@@ -143,22 +149,28 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 #pragma unroll
     for (int x = 0; x < SA_MAX_PER_LANE; ++x) acc[r][x] = 0.f;
   }
-  const int n_keys = i - lo + 1;
+  const int n_keys = npre + i - lo + 1;
   for (int j0 = warp * 32; j0 < n_keys; j0 += SA_WARPS * 32) {
-    const int j = lo + j0 + lane;
+    const int vi = j0 + lane;
+    const bool valid = vi < n_keys;
+    const int j = vi < npre ? vi : lo + vi - npre;
     float sc[REP], p[REP];
     int slot = 0;
 #pragma unroll
     for (int r = 0; r < REP; ++r) sc[r] = -INFINITY;
-    if (j <= i) {
+    if (valid) {
       slot = bt[j / page] * page + j % page;
       dot_rows<T, REP>(k_cache + static_cast<size_t>(slot) * nk + g * d, qs, d, qstride, vec, sc);
     }
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
-      const float s = j <= i ? sc[r] * scale : -INFINITY;
+      float s = -INFINITY;
+      if (valid) {
+        s = sc[r] * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      }
       const float m_new = fmaxf(m[r], warp_max(s));   // finite: the tile's first key exists
-      p[r] = j <= i ? expf(s - m_new) : 0.f;
+      p[r] = valid ? expf(s - m_new) : 0.f;
       const float corr = expf(m[r] - m_new);          // 0 on the first tile (m = -inf)
       l[r] = l[r] * corr + warp_sum(p[r]);
       m[r] = m_new;
@@ -173,7 +185,7 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
       for (int u = 0; u < SA_ROWS_AHEAD; ++u) {
         const int sk = __shfl_sync(0xffffffffu, slot, (kk0 + u) & 31);
         if (kk0 + u < cnt) {
-          load_cols<T>(v_cache + static_cast<size_t>(sk) * nv + g * dv + (room > 0 ? c_lane : 0), cpl, vbytes, room, vf[u]);
+          load_cols<T>(v_cache + static_cast<size_t>(sk) * nv + gv * dv + (room > 0 ? c_lane : 0), cpl, vbytes, room, vf[u]);
         } else {
 #pragma unroll
           for (int x = 0; x < SA_MAX_PER_LANE; ++x) vf[u][x] = 0.f;
@@ -231,20 +243,21 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 template <typename T, int REP>
 static void launch_sink_plain(cudaStream_t st, const void* q, const void* kc, const void* vc, void* out, const int32_t* tok_seq,
                               const int32_t* positions, const int32_t* seq_len, const int32_t* bt, int64_t bt_stride, const float* sink,
-                              const void* gate, int64_t ldg, int n_tokens, int H, int G, int d, int dv, int page, int mask_kind, int mask,
-                              float scale, int only_single) {
+                              const void* gate, int64_t ldg, int n_tokens, int H, int G, int Gv, int d, int dv, int page, int mask_kind,
+                              int mask, int keep_first, float softcap, float scale, int only_single) {
   const size_t sm = (static_cast<size_t>(REP) * ((d + 3) & ~3) + static_cast<size_t>(SA_WARPS) * REP * (dv + 2)) * sizeof(float);
   sink_attn_kernel<T, REP><<<dim3(n_tokens, H / REP), SA_WARPS * 32, sm, st>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), tok_seq, positions, seq_len, bt,
-      bt_stride, sink, static_cast<const T*>(gate), ldg, H, G, d, dv, page, mask_kind, mask, scale, only_single);
+      bt_stride, sink, static_cast<const T*>(gate), ldg, H, G, Gv, d, dv, page, mask_kind, mask, keep_first, softcap, scale, only_single);
 }
 
 template <typename T>
 static void launch_sink_plain_rep(int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                   const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_len, const int32_t* bt,
-                                  int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_tokens, int H, int G, int d,
-                                  int dv, int page, int mask_kind, int mask, float scale, int only_single) {
-#define SINK_PLAIN_ARGS st, q, kc, vc, out, tok_seq, positions, seq_len, bt, bt_stride, sink, gate, ldg, n_tokens, H, G, d, dv, page, mask_kind, mask, scale, only_single
+                                  int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_tokens, int H, int G, int Gv,
+                                  int d, int dv, int page, int mask_kind, int mask, int keep_first, float softcap, float scale,
+                                  int only_single) {
+#define SINK_PLAIN_ARGS st, q, kc, vc, out, tok_seq, positions, seq_len, bt, bt_stride, sink, gate, ldg, n_tokens, H, G, Gv, d, dv, page, mask_kind, mask, keep_first, softcap, scale, only_single
   // heads of a group that share a CTA: as many as divide the group, up to four (two for wide values: registers)
   if (rep % 4 == 0 && dv <= 128) launch_sink_plain<T, 4>(SINK_PLAIN_ARGS);
   else if (rep % 2 == 0) launch_sink_plain<T, 2>(SINK_PLAIN_ARGS);
@@ -266,8 +279,8 @@ __global__ void __launch_bounds__(SD_WARPS * 32)
 sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
                         const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int64_t bt_stride,
-                        const float* __restrict__ sink, const T* __restrict__ gate, int64_t ldg, int H, int G, int page,
-                        int mask_kind, int mask, float scale) {
+                        const float* __restrict__ sink, const T* __restrict__ gate, int64_t ldg, int H, int G, int Gv, int page,
+                        int mask_kind, int mask, int keep_first, float softcap, float scale) {
   constexpr int N = Vec16<T>::N, D = LPK * N, KPW = 32 / LPK;
   constexpr float LOG2E = 1.4426950408889634f;
   __shared__ float part[SD_WARPS][REP][D + 2];
@@ -281,7 +294,11 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   int lo = 0;
   if (mask > 0) lo = mask_kind == 0 ? max(0, i - mask + 1) : (i / mask) * mask;
   const int32_t* bt = block_tables + static_cast<int64_t>(b) * bt_stride;
-  const size_t row = static_cast<size_t>(G) * D;          // elements of a cached row (K and V alike: dv = d)
+  const size_t row = static_cast<size_t>(G) * D;          // elements of a cached key row
+  const size_t vrow = static_cast<size_t>(Gv) * D;        // and of a value row (dv = d)
+  const int gv = g % Gv;
+  const int npre = min(keep_first, lo), n_keys = npre + i - lo + 1;    // kept first keys the mask hides, then [lo, i]
+  const float cap2 = softcap * LOG2E;                      // the cap in the base-2 domain the scores live in
   float qv[REP][N], acc[REP][N], m[REP], l[REP];
 #pragma unroll
   for (int r = 0; r < REP; ++r) {
@@ -299,19 +316,20 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     }
   };
   constexpr int STEP = SD_WARPS * KPW;                     // keys the CTA takes per step
-  for (int j0 = lo; j0 <= i; j0 += STEP * SD_AHEAD) {
+  for (int j0 = 0; j0 < n_keys; j0 += STEP * SD_AHEAD) {
     uint4 kraw[SD_AHEAD], vraw[SD_AHEAD];
     bool ok[SD_AHEAD];
 #pragma unroll
     for (int u = 0; u < SD_AHEAD; ++u) {
-      const int j = j0 + u * STEP + warp * KPW + kg;
-      ok[u] = j <= i;
+      const int vi = j0 + u * STEP + warp * KPW + kg;
+      const int j = vi < npre ? vi : lo + vi - npre;
+      ok[u] = vi < n_keys;
       kraw[u] = vraw[u] = make_uint4(0, 0, 0, 0);
       if (ok[u]) {
         const int pg = j / page;
         const size_t slot = static_cast<size_t>(bt[pg]) * page + (j - pg * page);
         kraw[u] = ldg_v4(k_cache + slot * row + g * D + sub * N);
-        vraw[u] = ldg_v4(v_cache + slot * row + g * D + sub * N);
+        vraw[u] = ldg_v4(v_cache + slot * vrow + gv * D + sub * N);
       }
     }
     float sc[SD_AHEAD][REP];
@@ -326,6 +344,7 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
         for (int e = 0; e < N; ++e) s += f[e] * qv[r][e];
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (softcap > 0.f) s = cap2 * tanhf(s / cap2);
         sc[u][r] = ok[u] ? s : -INFINITY;
       }
     }
@@ -408,11 +427,11 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 template <typename T, int LPK>
 static void launch_sink_decode(int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
-                               int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int page,
-                               int mask_kind, int mask, float scale) {
+                               int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int Gv,
+                               int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
 #define SD_GO(REP) sink_attn_decode_kernel<T, LPK, REP><<<dim3(n_seqs, H / REP), SD_WARPS * 32, 0, st>>>(static_cast<const T*>(q), \
       static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, sink, \
-      static_cast<const T*>(gate), ldg, H, G, page, mask_kind, mask, scale)
+      static_cast<const T*>(gate), ldg, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale)
   if (rep % 4 == 0 && LPK * Vec16<T>::N <= 128) SD_GO(4);
   else if (rep % 2 == 0) SD_GO(2);
   else SD_GO(1);
@@ -423,11 +442,11 @@ static void launch_sink_decode(int rep, cudaStream_t st, const void* q, const vo
 template <typename T>
 static bool launch_sink_decode_any(int d, int dv, int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                    const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
-                                   int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G,
-                                   int page, int mask_kind, int mask, float scale) {
+                                   int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int Gv,
+                                   int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
   constexpr int N = Vec16<T>::N;
   if (d != dv || d % N != 0) return false;
-#define SD_ARGS rep, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, n_seqs, H, G, page, mask_kind, mask, scale
+#define SD_ARGS rep, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, n_seqs, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale
   switch (d / N) {
     case 4: launch_sink_decode<T, 4>(SD_ARGS); return true;
     case 8: launch_sink_decode<T, 8>(SD_ARGS); return true;
@@ -445,7 +464,9 @@ static bool launch_sink_decode_any(int d, int dv, int rep, cudaStream_t st, cons
 // l (both in the base-2 domain), rescales O when m grows, and the sink enters as the initial state m = sink, l = 1 with
 // no value.  Weights are computed in float from the float scores and enter the second product as a bf16 pair hi + lo
 // (lo = bf16(w - hi)), i.e. with 16 mantissa bits.  Both masks are a per-row lower bound lo(i) <= j <= i; tiles a warp
-// cannot see are skipped, tiles it sees whole take a path without per-element tests.
+// cannot see are skipped, tiles it sees whole take a path without per-element tests.  With kept first keys, tiles over
+// [0, min(F, lowest bound of the CTA)) run in front of the regular ones, and a regular tile that reaches below F is never
+// skipped.
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -469,15 +490,15 @@ sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                      const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                      const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int64_t bt_stride,
-                     const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int64_t ldg, int H, int G, int page,
-                     int mask_kind, int mask, float scale) {
+                     const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int64_t ldg, int H, int G, int Gv,
+                     int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
   constexpr int QS = D + 8, VS = DV + 8;             // padded rows: 16-byte aligned, ldmatrix rows land in distinct banks
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char sm_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(sm_raw);        // [BM][QS]
   __nv_bfloat16* Ks = Qs + SM_BM * QS;                                 // [2][BN][QS]
   __nv_bfloat16* Vs = Ks + 2 * SM_BN * QS;                             // [2][BN][VS]
-  const int b = blockIdx.z, h = blockIdx.y, g = h / (H / G);
+  const int b = blockIdx.z, h = blockIdx.y, g = h / (H / G), gv = g % Gv;
   const int len = seq_len[b];
   const int t0 = blockIdx.x * SM_BM;
   if (len <= 1 || t0 >= len) return;                 // one-token and padding rows belong to the plain kernel
@@ -490,7 +511,7 @@ sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     if (t0 + r < len) v = ldg_v4(q + (static_cast<size_t>(start + t0 + r) * H + h) * D + ch * 8);
     *reinterpret_cast<uint4*>(Qs + r * QS + ch * 8) = v;
   }
-  const float scale2 = scale * LOG2E;
+  const float scale2 = scale * LOG2E, cap2 = softcap * LOG2E;
   const int t_hi = min(len - 1, t0 + SM_BM - 1);
   const int j_lo = mask_lo(pos0 + t0, mask_kind, mask), j_hi = pos0 + t_hi;
   const int row_lo = wr * 16 + (lane >> 2);
@@ -513,16 +534,19 @@ sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 
   // two threads per key: the slot once, then the thread's 16-byte chunks lch, lch + 2, ... of the key's K and V rows
   const int lkey = tid >> 1, lch = tid & 1;
-  auto load_tile = [&](int stage, int j0) {
-    const int j = j0 + lkey;
-    const bool ok = j <= j_hi;
+  // kept first keys that the lowest bound of the CTA hides: tiles of their own, in front of the regular ones
+  const int pre_end = min(keep_first, j_lo), n_pre = (pre_end + SM_BN - 1) / SM_BN;
+  auto tile_j0 = [&](int t) { return t < n_pre ? t * SM_BN : j_lo + (t - n_pre) * SM_BN; };
+  auto load_tile = [&](int stage, int t) {
+    const int j = tile_j0(t) + lkey;
+    const bool ok = j <= (t < n_pre ? pre_end - 1 : j_hi);
     size_t slot = 0;
     if (ok) {
       const int pg = j / page;
       slot = static_cast<size_t>(bt[pg]) * page + (j - pg * page);
     }
     const __nv_bfloat16* ksrc = k_cache + (slot * G + g) * D + lch * 8;
-    const __nv_bfloat16* vsrc = v_cache + (slot * G + g) * DV + lch * 8;
+    const __nv_bfloat16* vsrc = v_cache + (slot * Gv + gv) * DV + lch * 8;
     __nv_bfloat16* kd = Ks + (stage * SM_BN + lkey) * QS + lch * 8;
     __nv_bfloat16* vd = Vs + (stage * SM_BN + lkey) * VS + lch * 8;
 #pragma unroll
@@ -530,18 +554,20 @@ sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 #pragma unroll
     for (int i = 0; i < DV / 16; ++i) cp_async_16(vd + i * 16, vsrc + i * 16, ok);
   };
-  const int n_tiles = (j_hi - j_lo) / SM_BN + 1;
-  load_tile(0, j_lo);
+  const int n_tiles = n_pre + (j_hi - j_lo) / SM_BN + 1;
+  load_tile(0, 0);
   cp_async_commit();
   for (int t = 0; t < n_tiles; ++t) {
-    const int j0 = j_lo + t * SM_BN;
+    const int j0 = tile_j0(t);
+    const bool pre = t < n_pre;
     cp_async_wait<0>();
     __syncthreads();                                 // tile t has landed (Q too); tile t - 1 is consumed
-    if (t + 1 < n_tiles) load_tile((t + 1) & 1, j0 + SM_BN);
+    if (t + 1 < n_tiles) load_tile((t + 1) & 1, t + 1);
     cp_async_commit();
     const __nv_bfloat16* Kt = Ks + (t & 1) * SM_BN * QS;
     const __nv_bfloat16* Vt = Vs + (t & 1) * SM_BN * VS;
-    if (j0 > wp_hi || j0 + SM_BN - 1 < w_first || t0 + wr * 16 >= len) continue;     // none of the warp's rows sees the tile
+    if (t0 + wr * 16 >= len) continue;
+    if (!pre && (j0 > wp_hi || (j0 + SM_BN - 1 < w_first && j0 >= keep_first))) continue;   // none of the warp's rows sees the tile
     float sacc[SM_BN / 8][4];
 #pragma unroll
     for (int i = 0; i < SM_BN / 8; ++i)
@@ -559,16 +585,19 @@ sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         mma_bf16_16816(sacc[2 * np + 1], a, b2, b3);
       }
     }
-    const bool inner = j0 + SM_BN - 1 <= wp_lo && j0 >= w_last;
+    const bool inner = !pre && j0 + SM_BN - 1 <= wp_lo && j0 >= w_last;
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
     for (int nt = 0; nt < SM_BN / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float s = sacc[nt][e] * scale2;
+        if (softcap > 0.f) s = cap2 * tanhf(s / cap2);
         if (!inner) {
           const int j = j0 + nt * 8 + 2 * (lane & 3) + (e & 1);
-          const bool ok = e < 2 ? (j <= p_lo && j >= lo_lo) : (j <= p_hi && j >= lo_hi);
+          bool ok;
+          if (pre) ok = j < pre_end;                 // below every row's bound and position: seen by all, counted here only
+          else ok = e < 2 ? (j <= p_lo && (j >= lo_lo || j < keep_first)) : (j <= p_hi && (j >= lo_hi || j < keep_first));
           if (!ok) s = -INFINITY;
         }
         sacc[nt][e] = s;
@@ -635,8 +664,8 @@ sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 template <int D, int DV>
 static cudaError_t launch_sink_mma(int max_new, int n_seqs, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                    const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
-                                   int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int H, int G, int page,
-                                   int mask_kind, int mask, float scale) {
+                                   int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int H, int G, int Gv, int page,
+                                   int mask_kind, int mask, int keep_first, float softcap, float scale) {
   auto kern = sink_attn_mma_kernel<D, DV>;
   const size_t smem = sizeof(__nv_bfloat16) * ((SM_BM + 2 * SM_BN) * (D + 8) + 2 * SM_BN * (DV + 8));
   static bool opted = false;
@@ -648,8 +677,8 @@ static cudaError_t launch_sink_mma(int max_new, int n_seqs, cudaStream_t st, con
   using B = __nv_bfloat16;
   const dim3 grid((max_new + SM_BM - 1) / SM_BM, H, n_seqs);
   kern<<<grid, 128, smem, st>>>(static_cast<const B*>(q), static_cast<const B*>(kc), static_cast<const B*>(vc), static_cast<B*>(out),
-                                seq_start, seq_pos0, seq_len, bt, bt_stride, sink, static_cast<const B*>(gate), ldg, H, G, page,
-                                mask_kind, mask, scale);
+                                seq_start, seq_pos0, seq_len, bt, bt_stride, sink, static_cast<const B*>(gate), ldg, H, G, Gv, page,
+                                mask_kind, mask, keep_first, softcap, scale);
   return cudaSuccess;
 }
 
@@ -658,12 +687,12 @@ static bool sink_mma_shape(int d, int dv) {
   return (d == 32 || d == 48 || d == 64 || d == 96 || d == 128) && (dv == 64 || dv == 128);
 }
 
-#define SINK_MMA_ARGS max_new, n_seqs, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, H, G, page, mask_kind, mask, scale
+#define SINK_MMA_ARGS max_new, n_seqs, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale
 template <int D>
 static cudaError_t launch_sink_mma_dv(int dv, int max_new, int n_seqs, cudaStream_t st, const void* q, const void* kc, const void* vc,
                                       void* out, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
                                       const int32_t* bt, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int H,
-                                      int G, int page, int mask_kind, int mask, float scale) {
+                                      int G, int Gv, int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
   return dv == 64 ? launch_sink_mma<D, 64>(SINK_MMA_ARGS) : launch_sink_mma<D, 128>(SINK_MMA_ARGS);
 }
 
@@ -676,8 +705,11 @@ using namespace b2::row;
 extern "C" int b2tts_sink_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* tok_seq,
                                const int32_t* positions, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
                                const int32_t* block_tables, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg,
-                               int n_tokens, int n_seqs, int max_new, int heads, int kv_heads, int dim, int vdim, int page,
-                               int mask_kind, int mask, float scale, int dtype, int path, void* stream) {
+                               int n_tokens, int n_seqs, int max_new, int heads, int kv_heads, int v_heads, int dim, int vdim, int page,
+                               int mask_kind, int mask, int keep_first, float softcap, float scale, int dtype, int path, void* stream) {
+  B2_REQUIRE(v_heads > 0 && kv_heads % v_heads == 0 && keep_first >= 0 && softcap >= 0.f, B2TTS_EINVAL,
+             "sink_attn: bad switches (v_heads=%d of kv_heads=%d, keep_first=%d, softcap=%g)", v_heads, kv_heads, keep_first, softcap);
+  if (mask <= 0) keep_first = 0;                     // nothing is hidden, nothing to keep
   B2_REQUIRE(n_tokens >= 0 && n_seqs >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && page > 0,
              B2TTS_EINVAL, "sink_attn: bad sizes (heads=%d kv_heads=%d dim=%d vdim=%d page=%d)", heads, kv_heads, dim, vdim, page);
   B2_REQUIRE(vdim <= 32 * SA_MAX_PER_LANE, B2TTS_EUNSUPPORTED, "sink_attn: value size %d above %d", vdim, 32 * SA_MAX_PER_LANE);
@@ -694,7 +726,7 @@ extern "C" int b2tts_sink_attn(const void* q, const void* k_cache, const void* v
   B2_REQUIRE(path != 2 || mma_ok, B2TTS_EUNSUPPORTED, "sink_attn: the tensor-core kernel takes bf16 with head sizes 32..128 / 64, 128");
   const bool use_mma = mma_ok && path != 1 && max_new > 1;
   if (use_mma) {
-    const int H = heads, G = kv_heads;
+    const int H = heads, G = kv_heads, Gv = v_heads;
     const void* kc = k_cache; const void* vc = v_cache; const int32_t* bt = block_tables;
     cudaError_t e;
     switch (dim) {
@@ -712,22 +744,23 @@ extern "C" int b2tts_sink_attn(const void* q, const void* k_cache, const void* v
   if (path != 1 && aligned16(q) && n_seqs > 0) {
     if (dtype == B2TTS_DTYPE_BF16)
       split = launch_sink_decode_any<__nv_bfloat16>(dim, vdim, heads / kv_heads, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
-                                                    block_tables, bt_stride, sink, gate, ldg, n_seqs, heads, kv_heads, page, mask_kind,
-                                                    mask, scale);
+                                                    block_tables, bt_stride, sink, gate, ldg, n_seqs, heads, kv_heads, v_heads, page, mask_kind,
+                                                    mask, keep_first, softcap, scale);
     else
       split = launch_sink_decode_any<float>(dim, vdim, heads / kv_heads, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
-                                            block_tables, bt_stride, sink, gate, ldg, n_seqs, heads, kv_heads, page, mask_kind, mask,
-                                            scale);
+                                            block_tables, bt_stride, sink, gate, ldg, n_seqs, heads, kv_heads, v_heads, page, mask_kind, mask,
+                                            keep_first, softcap, scale);
     if (split) B2_CHECK_LAUNCH("sink_attn (one-token rows)");
   }
   const int skip = (use_mma ? 1 : 0) | (split ? 2 : 0);
   if (dtype == B2TTS_DTYPE_BF16)
     launch_sink_plain_rep<__nv_bfloat16>(heads / kv_heads, st, q, k_cache, v_cache, out, tok_seq, positions, seq_len, block_tables,
-                                         bt_stride, sink, gate, ldg, n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale,
-                                         skip);
+                                         bt_stride, sink, gate, ldg, n_tokens, heads, kv_heads, v_heads, dim, vdim, page, mask_kind, mask,
+                                         keep_first, softcap, scale, skip);
   else
     launch_sink_plain_rep<float>(heads / kv_heads, st, q, k_cache, v_cache, out, tok_seq, positions, seq_len, block_tables, bt_stride,
-                                 sink, gate, ldg, n_tokens, heads, kv_heads, dim, vdim, page, mask_kind, mask, scale, skip);
+                                 sink, gate, ldg, n_tokens, heads, kv_heads, v_heads, dim, vdim, page, mask_kind, mask, keep_first,
+                                 softcap, scale, skip);
   B2_CHECK_LAUNCH("sink_attn");
   return B2TTS_OK;
 }

@@ -44,6 +44,19 @@ class XIELU(nn.Module):
         return nat.xielu_(y, bias, self.pq)
 
 
+class PolyNorm(nn.Module):
+    """a N(z) + b N(z^2) + c N(z^3) + e with four learned numbers kept in float; powers element by element, N divides a
+    row by its root mean square (eps inside the root); in place."""
+
+    def __init__(self, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+        self.coef = nn.Parameter(torch.zeros(4, dtype=torch.float32), requires_grad=False)
+
+    def forward(self, y: torch.Tensor) -> torch.Tensor:
+        return nat.polynorm_(y, self.coef, self.eps)
+
+
 class GatedSilu(nn.Module):
     """[gate | up] along the last axis -> silu(gate) * up (bf16 or float32)."""
 

@@ -111,17 +111,27 @@ class SinkSoftmaxAttention(nn.Module):
     ``prepare`` turns the mixer's merged projection into queries and cache rows: optional biases, optional RMS norm over
     the whole q and the whole k projection, optional half-split rotation; the values are a projection of their own or,
     with ``v_off`` < 0, the keys as projected.  ``forward`` attends; an optional per-head sigmoid gate rides in the same
-    launch.  The cache holds this step's keys already, so prompt portions and decoded tokens share the launch."""
+    launch.  The cache holds this step's keys already, so prompt portions and decoded tokens share the launch.
+
+    Further switches: ``sink`` "learned" (a parameter per head), "zero" (the denominator gets exp(0) = 1: the parameter
+    stays zero and is not part of a checkpoint) or "none" (an ordinary softmax); ``softcap`` c > 0 turns a scaled score s
+    into c tanh(s / c); ``keep_first`` keys stay visible behind the mask; ``mask`` 0 is plain causal attention; the
+    rotation pairs coordinate i with i + dims/2 or 2i with 2i + 1 as the ``rotary`` module says; ``v_heads`` < ``kv_heads``
+    value heads are shared by the key heads (key head g reads value head g mod v_heads); ``own_cache`` False: the
+    module projects no keys and values and reads a cache another module writes."""
 
     MASKS = {"window": nat.MASK_WINDOW, "chunk": nat.MASK_CHUNK}
 
     def __init__(self, heads: int, kv_heads: int, dim: int, vdim: int, mask_kind: str, mask: int, scale: float, *,
-                 bias: bool = False, qk_norm: bool = False, rotary=None, eps: float = 1e-6):
+                 bias: bool = False, qk_norm: bool = False, rotary=None, eps: float = 1e-6, sink: str = "learned",
+                 softcap: float = 0.0, keep_first: int = 0, v_heads: int | None = None, own_cache: bool = True):
         super().__init__()
+        assert sink in ("learned", "zero", "none")
         self.heads, self.kv_heads, self.dim, self.vdim, self.scale, self.eps = heads, kv_heads, dim, vdim, scale, eps
         self.mask_kind, self.mask, self.rotary = self.MASKS[mask_kind], mask, rotary
+        self.softcap, self.keep_first, self.v_heads, self.own_cache = softcap, keep_first, v_heads or kv_heads, own_cache
         f32 = dict(dtype=torch.float32)
-        self.sink = nn.Parameter(torch.zeros(heads, **f32), requires_grad=False)
+        self.sink = nn.Parameter(torch.zeros(heads, **f32), requires_grad=False) if sink != "none" else None
         mk = lambda n, one: nn.Parameter((torch.ones if one else torch.zeros)(n, **f32), requires_grad=False)
         self.q_bias = mk(heads * dim, False) if bias else None
         self.k_bias = mk(kv_heads * dim, False) if bias else None
@@ -134,14 +144,53 @@ class SinkSoftmaxAttention(nn.Module):
         lay = get_context().step_layout
         q = torch.empty(u.shape[0], self.heads * self.dim, dtype=u.dtype, device=u.device)
         rot = self.rotary
+        own = self.own_cache
         nat.attn_prep(u, q_off, k_off, v_off, self.q_bias, self.k_bias, self.v_bias if v_off >= 0 else None, self.q_norm,
                       self.k_norm, rot.freq if rot is not None else None, rot.dims if rot is not None else 0, lay, q,
-                      self.k_cache, self.v_cache, self.heads, self.kv_heads, self.dim, self.vdim, self.eps)
+                      self.k_cache if own else None, self.v_cache if own else None, self.heads, self.kv_heads, self.dim,
+                      self.vdim, self.eps, interleaved=rot is not None and rot.interleaved, v_heads=self.v_heads)
         return q
 
     def forward(self, q: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
         lay = get_context().step_layout
         out = torch.empty(q.shape[0], self.heads * self.vdim, dtype=q.dtype, device=q.device)
         nat.sink_attn(q, self.k_cache, self.v_cache, out, lay, self.sink, gate, self.heads, self.kv_heads, self.dim, self.vdim,
-                      self.k_cache.shape[1], self.mask_kind, self.mask, self.scale)
+                      self.k_cache.shape[1], self.mask_kind, self.mask, self.scale, v_heads=self.v_heads,
+                      keep_first=self.keep_first, softcap=self.softcap)
         return out
+
+
+class DifferentialAttention(SinkSoftmaxAttention):
+    """Two softmax maps per head over the same values, combined as map 1 - lambda * map 2, each head's result divided by
+    its root mean square and multiplied by ``1 - diff``; lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff is one number per
+    layer.  The maps run as ``2 * heads`` query heads over ``2 * kv_heads`` key heads that share ``kv_heads`` value heads;
+    queries and keys are expected MAP-MAJOR (all heads of map 1, then all heads of map 2), which makes the grouping of
+    query heads over key heads the ordinary one: a model permutes the projection's rows once when it loads them
+    (``map_major``).  No positions enter; the mask is causal, a sliding window, optionally with kept first keys."""
+
+    def __init__(self, heads: int, kv_heads: int, dim: int, vdim: int, window: int, keep_first: int, scale: float, diff: float,
+                 eps: float = 1e-6, own_cache: bool = True):
+        super().__init__(2 * heads, 2 * kv_heads, dim, vdim, "window", window, scale, eps=eps, sink="none", keep_first=keep_first,
+                         v_heads=kv_heads, own_cache=own_cache)
+        self.out_heads, self.diff = heads, diff
+        f32 = dict(dtype=torch.float32)
+        for name in ("lq1", "lk1", "lq2", "lk2"):
+            setattr(self, name, nn.Parameter(torch.zeros(dim, **f32), requires_grad=False))
+        self._lam = None
+
+    @staticmethod
+    def map_major(w: torch.Tensor, heads: int, dim: int) -> torch.Tensor:
+        """Rows [head][map][dim] of a q or k projection -> [map][head][dim]."""
+        return w.reshape(heads, 2, dim, -1).transpose(0, 1).reshape(w.shape)
+
+    def lam(self) -> float:
+        """lambda in float, computed once from the loaded vectors."""
+        if self._lam is None:
+            a = torch.exp((self.lq1.float() * self.lk1.float()).sum()) - torch.exp((self.lq2.float() * self.lk2.float()).sum())
+            self._lam = float(a.item() + self.diff)
+        return self._lam
+
+    def forward(self, q: torch.Tensor) -> torch.Tensor:
+        maps = super().forward(q)
+        out = torch.empty(q.shape[0], self.out_heads * self.vdim, dtype=q.dtype, device=q.device)
+        return nat.diff_combine(maps, out, self.lam(), 1.0 - self.diff, self.out_heads, self.vdim, self.eps)

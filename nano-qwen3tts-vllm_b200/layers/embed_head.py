@@ -56,6 +56,24 @@ class ScaledTokenEmbedding(nn.Module):
         return x
 
 
+class NormedTokenEmbedding(nn.Module):
+    """Token embedding followed by a single-gain RMS norm, written as floats into a 32-bit residual stream; the first
+    layer's input norm rides in the same launch."""
+
+    def __init__(self, vocab: int, width: int, eps: float = 1e-6):
+        super().__init__()
+        from .layernorm import GainRMSNorm
+        self.embed = nn.Parameter(torch.empty(vocab, width), requires_grad=False)
+        self.norm = GainRMSNorm(eps)
+
+    def forward(self, tokens: torch.Tensor, next_norm=None):
+        """-> (x [n, width] float, the next sublayer's input in the table's dtype or None)."""
+        x = torch.empty(tokens.shape[0], self.embed.shape[1], dtype=torch.float32, device=tokens.device)
+        h = nat.sandwich_residual(x, self.norm.gain(), a=self.embed, a_index=tokens, init=True, eps=self.norm.eps,
+                                  g_in=next_norm.gain() if next_norm is not None else None)
+        return x, h
+
+
 class BigramTokenEmbedding(nn.Module):
     """Token embedding plus a row of a hashed bigram table, row (previous token * mul_prev + token * mul_cur) mod
     ``buckets`` (the table's extra last row for a sequence's first token), written as floats into every one of

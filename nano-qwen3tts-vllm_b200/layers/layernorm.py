@@ -45,6 +45,23 @@ class GainRMSNorm(nn.Module):
         return nat.gather_gain_norm(x, rows, self.gain(), self.eps, dtype)
 
 
+class SandwichNorm(nn.Module):
+    """The pair of single-gain RMS norms around a sublayer whose output is normed before it joins a 32-bit residual
+    stream: ``self.pre`` on the way in, ``self.post`` on the way out.  ``add`` does x += post(y) and returns the NEXT
+    sublayer's input ``nxt.pre(x)`` from the same launch (``nat.sandwich_residual``).  y is a dense output ``a``; two
+    branch outputs ``a``, ``b`` that are first RMS-normed over the row with weight vectors ``wa``, ``wb`` and summed with
+    ``branch_scale``; or per-choice expert outputs ``z`` with weights ``zw``, where choices ``z_idx`` >= ``n_real`` stand
+    for identity experts and contribute the sublayer's input ``hin``."""
+
+    def __init__(self, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+        self.pre, self.post = GainRMSNorm(eps), GainRMSNorm(eps)
+
+    def add(self, x: torch.Tensor, nxt: "GainRMSNorm | None", **y) -> torch.Tensor | None:
+        return nat.sandwich_residual(x, self.post.gain(), g_in=nxt.gain() if nxt is not None else None, eps=self.eps, **y)
+
+
 class GroupRMSNorm(nn.Module):
     """RMS norm in groups: the vector is cut into ``groups`` equal consecutive parts, each divided by its own
     sqrt(mean(part^2) + eps), the whole multiplied by a weight vector (kept in float).  In a model it sits on a

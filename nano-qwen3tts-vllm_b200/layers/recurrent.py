@@ -128,3 +128,44 @@ class DeltaRuleMemory(nn.Module):
         out = torch.empty(n, hv, dtype=u.dtype, device=u.device)
         nat.gated_group_norm(o, u[:, cols["g"]:cols["g"] + hv], self.norm, m.heads, nat.GATE_SILU, False, self.eps, out)
         return out
+
+
+class GatedLinearAttention(nn.Module):
+    """Gated linear attention: S <- diag(alpha) S + k v^T, o = S^T q per head, q scaled by dim^(-1/2), with one decay per
+    key channel and token alpha = sigmoid(W_a2 (W_a1 h) + b)^(1/tau).  The first step of the decay projection rides in
+    the mixer's merged input projection (part ``a1``), the second is a small GEMM of this module; bias, logsigmoid,
+    the division by tau and the exponential are float.  Each head's read-out is RMS-normed with a weight shared by the
+    heads, then multiplied by silu(W_g h)."""
+
+    def __init__(self, spec, eps: float):
+        super().__init__()
+        m = self.spec = spec
+        assert m.decay_rank > 0, "the decay projection's inner size is unknown (read it from the checkpoint's tensor shapes)"
+        self.eps = eps
+        self.a2 = nn.Parameter(torch.empty(m.heads * m.dim, m.decay_rank), requires_grad=False)
+        self.a2_bias = nn.Parameter(torch.zeros(m.heads * m.dim, **F32), requires_grad=False)
+        self.norm = nn.Parameter(torch.ones(m.vdim, **F32), requires_grad=False)
+        self.S = None
+
+    def proj_parts(self):
+        m = self.spec
+        return [("q", m.heads * m.dim), ("k", m.heads * m.dim), ("v", m.heads * m.vdim), ("g", m.heads * m.vdim), ("a1", m.decay_rank)]
+
+    def state_plan(self):
+        m = self.spec
+        return [((m.heads, m.dim, m.vdim), torch.float32)]
+
+    def bind(self, state):
+        (self.S,) = state
+
+    def forward(self, u: torch.Tensor, cols: dict) -> torch.Tensor:
+        from .linear import linear
+        m, lay = self.spec, get_context().step_layout
+        n, hd, hv = u.shape[0], m.heads * m.dim, m.heads * m.vdim
+        cut = lambda name, w: u[:, cols[name]:cols[name] + w]
+        z = linear(cut("a1", m.decay_rank).contiguous(), self.a2)
+        o = torch.empty(n, hv, dtype=torch.float32, device=u.device)
+        nat.gated_linear_scan(cut("q", hd), cut("k", hd), cut("v", hv), z, self.a2_bias, m.tau, self.S, o, lay, m.heads, m.dim, m.vdim)
+        out = torch.empty(n, hv, dtype=u.dtype, device=u.device)
+        nat.gated_group_norm(o, cut("g", hv), self.norm, m.heads, nat.GATE_SILU, False, self.eps, out)
+        return out

@@ -74,6 +74,7 @@ class PairRotary(nn.Module):
     turns(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(turns(fast)), 0),
     hi = min(ceil(turns(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is
     f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by ``mult`` = 0.1 ln(factor) + 1.
+    With ``scaling`` = {factor} alone (linear): f_i / factor, ``mult`` stays 1.
     The table is computed in float64 and kept as float; the kernels that rotate (``nat.latent_prep`` for keys,
     ``nat.latent_attn`` for queries) form the angle position * f_i in float."""
 
@@ -84,7 +85,9 @@ class PairRotary(nn.Module):
         i = torch.arange(dims // 2, dtype=torch.float64)
         f = torch.as_tensor(float(base), dtype=torch.float64) ** (-2.0 * i / max(dims, 1))
         self.dims, self.mult = dims, 1.0
-        if scaling:
+        if scaling and "original" not in scaling:
+            f = f / float(scaling["factor"])
+        elif scaling:
             factor, orig = float(scaling["factor"]), float(scaling["original"])
             turns = lambda t: dims * math.log(orig / (2 * math.pi * t)) / (2 * math.log(base))
             lo = max(math.floor(turns(float(scaling["fast"]))), 0)
@@ -93,6 +96,8 @@ class PairRotary(nn.Module):
             f = f / factor * ramp + f * (1 - ramp)
             self.mult = 0.1 * math.log(factor) + 1.0
         self.register_buffer("freq", f.to(torch.float32), persistent=False)
+
+    interleaved = True
 
 
 class HalfRotary(nn.Module):
@@ -107,3 +112,5 @@ class HalfRotary(nn.Module):
         f = torch.as_tensor(float(base), dtype=torch.float64) ** (-2.0 * i / max(dims, 1))
         self.dims = dims
         self.register_buffer("freq", f.to(torch.float32), persistent=False)
+
+    interleaved = False

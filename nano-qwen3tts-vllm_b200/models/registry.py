@@ -58,6 +58,9 @@ register(Architecture("Ridevik", ".config:RidevikConfig", ".models.ridevik:Ridev
 register(Architecture("Tibivik", ".config:TibivikConfig", ".models.tibivik:TibivikForCausalLM",
                       ".engine.model_runner.lm_model_runner:LMModelRunner",
                       ".engine.llm_engine.lm_engine:CausalLMEngine"))
+register(Architecture("Teberax", ".config:TeberaxConfig", ".models.teberax:TeberaxForCausalLM",
+                      ".engine.model_runner.lm_model_runner:LMModelRunner",
+                      ".engine.llm_engine.lm_engine:CausalLMEngine"))
 
 
 def resolve(config: dict) -> Architecture:
