@@ -227,3 +227,103 @@ def forward(cfg: dict, sd: dict, tokens, trace=None):
     logits = rms_norm(x, sd["final.norm"], eps) @ sd["head"].T
     cap = cfg.get("logit_softcap")
     return cap * torch.tanh(logits / cap) if cap else logits
+
+
+# ------------------------------------------------------------------------------------------------ small random models
+def random_config(vocab=61, width=24, types=("parallel", "latent_attention", "attention", "attention"), kv_from=None,
+                  ff=("dense", "moe", "moe", None), logit_softcap=9.0, eps=1e-5, attention=None, left=None, right=None,
+                  latent=None, moe=None, dense_ff=20) -> dict:
+    """A small configuration in the checkpoint's format.  ``types``: the mixers in order; ``kv_from``: {layer: source};
+    ``ff``: per layer "dense", "moe" or None; the dicts override fields of the matching mixer / feed-forward."""
+    att = dict(heads=4, kv_heads=2, dim=6, vdim=10, diff=0.3, scale=0.5, mask={"size": 9, "keep_first": 2})
+    att.update(attention or {})
+    lf = dict(heads=4, kv_heads=2, dim=8, vdim=6, scale=0.4, softcap=3.0, rot={"dims": 4, "base": 100.0, "scaling": {"factor": 4.0}})
+    lf.update(left or {})
+    rt = dict(heads=2, dim=5, vdim=7, tau=4.0, decay_rank=3)
+    rt.update(right or {})
+    lat = dict(heads=3, dim=6, rot_dim=4, vdim=5, kv_rank=12, scale=0.35, mask={"size": 11}, rot={"dims": 4, "base": 50.0})
+    lat.update(latent or {})
+    me = dict(kind="moe", expert={"ff": 10}, router={"experts": 5, "identity": 2, "top": 3})
+    me.update(moe or {})
+    layers = []
+    for i, kind in enumerate(types):
+        if kind == "attention":
+            m = dict(att)
+            if kv_from and i in kv_from:
+                m["kv_from"] = kv_from[i]
+        elif kind == "parallel":
+            m = {"left": dict(lf), "right": dict(rt)}
+        else:
+            m = dict(lat)
+        f = ff[i % len(ff)]
+        mlp = None if f is None else ({"kind": "dense", "ff": dense_ff} if f == "dense" else dict(me))
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    out = {"architecture": "Teberax", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if logit_softcap:
+        out["logit_softcap"] = logit_softcap
+    return out
+
+
+def tensor_shapes(cfg: dict) -> dict:
+    D, sh = cfg["width"], {"embed": (cfg["vocab"], cfg["width"]), "embed.norm": (), "final.norm": (), "head": (cfg["vocab"], cfg["width"])}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        sh[p + "norm1"] = sh[p + "norm1b"] = ()
+        if layer["type"] == "attention":
+            sh[p + "mix.q"] = (m["heads"] * 2 * m["dim"], D)
+            if m.get("kv_from") is None:
+                sh[p + "mix.k"], sh[p + "mix.v"] = (m["kv_heads"] * 2 * m["dim"], D), (m["kv_heads"] * m["vdim"], D)
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                sh[p + "mix." + n] = (m["dim"],)
+            sh[p + "mix.o"] = (D, m["heads"] * m["vdim"])
+        elif layer["type"] == "parallel":
+            a, r = m["left"], m["right"]
+            for n, rows in (("q", a["heads"] * a["dim"]), ("k", a["kv_heads"] * a["dim"]), ("v", a["kv_heads"] * a["vdim"])):
+                sh[f"{p}mix.left.{n}"], sh[f"{p}mix.left.{n}.b"] = (rows, D), (rows,)
+            sh[p + "mix.left.o"], sh[p + "mix.left.o.b"], sh[p + "mix.left.out"] = (D, a["heads"] * a["vdim"]), (D,), (D,)
+            hd, hv, rk = r["heads"] * r["dim"], r["heads"] * r["vdim"], r["decay_rank"]
+            for n, rows in (("q", hd), ("k", hd), ("v", hv), ("g", hv), ("a1", rk)):
+                sh[f"{p}mix.right.{n}"] = (rows, D)
+            sh[p + "mix.right.a2"], sh[p + "mix.right.a2.b"], sh[p + "mix.right.norm"] = (hd, rk), (hd,), (r["vdim"],)
+            sh[p + "mix.right.o"], sh[p + "mix.right.out"] = (D, hv), (D,)
+        else:
+            sh[p + "mix.q"], sh[p + "mix.dkv"] = (m["heads"] * (m["dim"] + m["rot_dim"]), D), (m["kv_rank"] + m["rot_dim"], D)
+            sh[p + "mix.dkv.norm"] = (m["kv_rank"],)
+            sh[p + "mix.uk"], sh[p + "mix.uv"] = (m["heads"] * m["dim"], m["kv_rank"]), (m["heads"] * m["vdim"], m["kv_rank"])
+            sh[p + "mix.o"] = (D, m["heads"] * m["vdim"])
+        f = layer.get("mlp")
+        if f is None:
+            continue
+        sh[p + "norm2"] = sh[p + "norm2b"] = ()
+        if f["kind"] == "dense":
+            sh[p + "mlp.up"], sh[p + "mlp.down"], sh[p + "mlp.act"] = (f["ff"], D), (D, f["ff"]), (4,)
+        else:
+            n_out = f["router"]["experts"] + f["router"].get("identity", 0)
+            sh[p + "mlp.router"], sh[p + "mlp.correction"] = (n_out, D), (n_out,)
+            for e in range(f["router"]["experts"]):
+                sh[f"{p}mlp.e{e}.gate"] = sh[f"{p}mlp.e{e}.up"] = (f["expert"]["ff"], D)
+                sh[f"{p}mlp.e{e}.down"] = (D, f["expert"]["ff"])
+    return sh
+
+
+def random_weights(cfg: dict, seed: int = 0) -> dict:
+    """Random tensors under the checkpoint's names, rounded to bfloat16 (what a file would hold), returned as float64."""
+    g = torch.Generator().manual_seed(seed)
+    sd = {}
+    for name, shape in sorted(tensor_shapes(cfg).items()):
+        leaf = name.rsplit(".", 1)[-1]
+        t = torch.randn(shape, generator=g)
+        if len(shape) == 0:
+            t = 1.0 + 0.2 * t
+        elif len(shape) == 2:
+            t = t * (1.5 if leaf == "router" else 1.0) * shape[1] ** -0.5
+        elif leaf in ("norm", "out"):
+            t = 1.0 + 0.2 * t
+        elif leaf == "act":
+            t = torch.tensor([1.0, 0.4, 0.2, 0.1]) + 0.1 * t
+        elif leaf == "correction":
+            t = 0.05 * t
+        else:
+            t = 0.4 * t
+        sd[name] = t.to(torch.bfloat16).double()
+    return sd
