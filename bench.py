@@ -63,6 +63,10 @@ def parse():
     ap.add_argument("--lm-hybrid", action="store_true",
                     help="instead of the frame loop: the Tibivik decoder (residual streams, attention beside recurrences) beside "
                          "Bokenex at equal layer sizes, plus the kernels of both against their rooflines (bench_lm.py); one JSON line")
+    ap.add_argument("--lm-teberax", action="store_true",
+                    help="instead of the frame loop: the Teberax decoder (differential, biased rotary + gated linear, latent "
+                         "attention; in-and-out norms) beside Tibivik at equal layer sizes, plus the kernels of both against their "
+                         "rooflines (bench_lm.py); one JSON line")
     return ap.parse_args()
 
 
@@ -486,10 +490,11 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(device))
     barrier = (lambda: (dist.barrier(), torch.cuda.synchronize())) if dist else None
 
-    if a.lm or a.lm_latent or a.lm_hybrid:
+    if a.lm or a.lm_latent or a.lm_hybrid or a.lm_teberax:
         import bench_lm
         if rank == 0:
-            run = bench_lm.main_hybrid if a.lm_hybrid else bench_lm.main_latent if a.lm_latent else bench_lm.main
+            run = bench_lm.main_teberax if a.lm_teberax else bench_lm.main_hybrid if a.lm_hybrid else bench_lm.main_latent if a.lm_latent \
+                else bench_lm.main
             print(json.dumps(run(device)), flush=True)
         return
 

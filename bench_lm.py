@@ -68,7 +68,7 @@ def bench_bokenex(s: dict, moe: bool, device: str, design: str = "bokenex") -> d
     import torch
     from nano_qwen3tts_vllm_b200.engine.llm_engine.lm_engine import CausalLMEngine
     from nano_qwen3tts_vllm_b200.sampling_params import SamplingParams
-    cfg = {"bokenex": bokenex_config, "ridevik": ridevik_config, "tibivik": tibivik_config}[design](s, moe)
+    cfg = {"bokenex": bokenex_config, "ridevik": ridevik_config, "tibivik": tibivik_config, "teberax": teberax_config}[design](s, moe)
     pages = DECODE_SEQS * ((DECODE_CTX + 64 + PAGE - 1) // PAGE) + PREFILL_SEQS * (PREFILL_LEN // PAGE + 1)
     eng = CausalLMEngine(cfg, state_dict="random:7", kvcache_block_size=PAGE, num_kvcache_blocks=pages,
                          max_num_seqs=DECODE_SEQS + PREFILL_SEQS, max_model_len=4096, max_num_batched_tokens=16384,
@@ -573,6 +573,188 @@ def bench_hybrid_kernels(device: str) -> dict:
     ms = timed(lambda: nat.gated_group_norm(yy, gg, wn, H, nat.GATE_SILU, False, 1e-6, oo))
     res["gated_group_norm 8192x2048 (16 heads)"] = entry(ms, bytes_=n * H * d * (4 + 2 + 2))
     return res
+
+
+def teberax_config(s: dict, moe: bool = True):
+    """Layers of real models' shapes at the size's width: biased rotary attention of the size's head layout (causal, capped
+    scores, zero sink) beside gated linear attention of half as many heads of 128 x 128; windowed latent attention over a
+    latent of 4 head sizes; differential attention whose two maps of half a head size share values of a full head size,
+    window with four kept first keys, the second such layer on the first one's keys and values.  Feed-forwards: dense
+    PolyNorm with two matrices of the talker's parameter count, or 16 SiLU-gated experts (top 2) and one identity expert."""
+    from nano_qwen3tts_vllm_b200.config import TeberaxConfig
+    d, H, G, W = s["dim"], s["heads"], s["kv_heads"], s["width"]
+    ff = s["inter"] * 3 // 2
+    dense = {"kind": "dense", "ff": ff}
+    experts = {"kind": "moe", "expert": {"ff": ff // 3}, "router": {"experts": 16, "identity": 1, "top": 2}} if moe else dense
+    par = {"type": "parallel", "mlp": dense,
+           "mixer": {"left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 50.0,
+                              "rot": {"dims": d // 2, "base": 1e4, "scaling": {"factor": 2.0}}},
+                     "right": {"heads": H // 2, "dim": d, "vdim": d, "tau": 16.0, "decay_rank": 16}}}
+    lat = {"type": "latent_attention", "mlp": experts,
+           "mixer": {"heads": H, "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": 4 * d, "scale": (d + d // 2) ** -0.5,
+                     "mask": {"size": WINDOW}, "rot": {"dims": d // 2, "base": 1e4}}}
+    att = {"heads": H, "kv_heads": G, "dim": d // 2, "vdim": d, "scale": (d // 2) ** -0.5, "diff": 0.5, "mask": {"size": WINDOW, "keep_first": 4}}
+    own = {"type": "attention", "mlp": experts, "mixer": att}
+    borrowed = {"type": "attention", "mlp": dense, "mixer": dict(att, kv_from=2)}
+    return TeberaxConfig.from_dict({"architecture": "Teberax", "vocab": 3072, "width": W, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+                                    "layers": [par, lat, own, borrowed][:LAYERS]})
+
+
+def bench_teberax_kernels(device: str) -> dict:
+    """The kernels Teberax added or extended at the w2048 layer shapes, each after an L2 flush, with the fraction of the
+    measured roofline; the like kernels of Tibivik come from ``bench_hybrid_kernels`` in the same run."""
+    import torch
+    import nano_qwen3tts_vllm_b200._native as nat
+    hbm, tflops, how = _peaks()
+    dev = torch.device(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    BF = torch.bfloat16
+
+    def timed(fn, iters=5):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    class Lay:
+        pass
+
+    def layout(n_seqs, cached, new, pages_per_seq):
+        lay = Lay()
+        i32 = dict(dtype=torch.int32, device=dev)
+        lay.n_seqs, lay.max_new, lay.n_tokens = n_seqs, new, n_seqs * new
+        lay.seq_start = torch.arange(n_seqs, **i32) * new
+        lay.seq_pos0 = torch.full((n_seqs,), cached, **i32)
+        lay.seq_len = torch.full((n_seqs,), new, **i32)
+        lay.seq_slot = torch.arange(n_seqs, **i32)
+        lay.block_tables = torch.arange(n_seqs * pages_per_seq, **i32).view(n_seqs, pages_per_seq).contiguous()
+        pos = (torch.arange(new, **i32) + cached).repeat(n_seqs)
+        lay.positions = pos
+        lay.tok_seq = torch.arange(n_seqs, **i32).repeat_interleave(new)
+        lay.slot_mapping = (lay.tok_seq * pages_per_seq * PAGE + pos).to(torch.int32)
+        return lay
+
+    def entry(ms, bytes_=None, flops=None):
+        e = {"us": round(ms * 1e3, 1)}
+        if bytes_ is not None:
+            e["gbs"] = round(bytes_ / ms / 1e6, 1)
+            e["frac_hbm"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 1)
+            e["frac_tensor"] = round(flops / ms / 1e9 / tflops, 4)
+        return e
+
+    H, G, d, D = 16, 8, 128, 2048
+    res = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how}}
+    pps = (DECODE_CTX + PAGE) // PAGE + 1
+    dlay = layout(DECODE_SEQS, DECODE_CTX, 1, pps)
+    play = layout(PREFILL_SEQS, 0, PREFILL_LEN, PREFILL_LEN // PAGE)
+    n = PREFILL_SEQS * PREFILL_LEN
+    # ---- biased rotary branch: causal, capped scores, zero sink (heads 16 over 8, 128 x 128)
+    kc = torch.randn(DECODE_SEQS * pps, PAGE, G * d, device=dev).to(BF)
+    vc = torch.randn(DECODE_SEQS * pps, PAGE, G * d, device=dev).to(BF)
+    zero = torch.zeros(H, device=dev)
+
+    def left(lay):
+        q = torch.randn(lay.n_tokens, H * d, device=dev).to(BF)
+        out = torch.empty(lay.n_tokens, H * d, dtype=BF, device=dev)
+        return lambda: nat.sink_attn(q, kc, vc, out, lay, zero, None, H, G, d, d, PAGE, nat.MASK_WINDOW, 0, d ** -0.5, softcap=50.0)
+
+    res["sink_attn decode 64x1100 causal, cap, zero sink"] = entry(timed(left(dlay)), bytes_=DECODE_SEQS * (DECODE_CTX + 1) * G * d * 2 * 2)
+    pairs = PREFILL_SEQS * sum(i + 1 for i in range(PREFILL_LEN))
+    res["sink_attn prefill 4x2048 causal, cap, zero sink"] = entry(timed(left(play), iters=3), flops=pairs * H * 2 * d * 2)
+    # ---- differential attention: 2 x 16 query heads of 64 over 2 x 8 key heads, 8 value heads of 128, window 1024 + 4 kept
+    dq = d // 2
+    kc2 = torch.randn(DECODE_SEQS * pps, PAGE, 2 * G * dq, device=dev).to(BF)
+
+    def diff(lay):
+        q = torch.randn(lay.n_tokens, 2 * H * dq, device=dev).to(BF)
+        maps = torch.empty(lay.n_tokens, 2 * H * d, dtype=BF, device=dev)
+        return maps, (lambda: nat.sink_attn(q, kc2, vc, maps, lay, None, None, 2 * H, 2 * G, dq, d, PAGE, nat.MASK_WINDOW, WINDOW, dq ** -0.5,
+                                            v_heads=G, keep_first=4))
+
+    res["sink_attn decode 64x1100 two maps, window 1024 + 4 kept"] = entry(timed(diff(dlay)[1]),
+                                                                          bytes_=DECODE_SEQS * (WINDOW + 4) * (2 * G * dq + G * d) * 2)
+    pairs_w = PREFILL_SEQS * sum(min(i + 1, WINDOW + 4) for i in range(PREFILL_LEN))
+    maps, fn = diff(play)
+    res["sink_attn prefill 4x2048 two maps, window 1024 + 4 kept"] = entry(timed(fn, iters=3), flops=pairs_w * 2 * H * 2 * (dq + d))
+    oc = torch.empty(n, H * d, dtype=BF, device=dev)
+    res["diff_combine 8192 tokens x 16 heads x 128"] = entry(timed(lambda: nat.diff_combine(maps, oc, 0.3, 0.5, H, d, 1e-6)),
+                                                            bytes_=n * H * d * 3 * 2)
+    # ---- attention preparation: biases, interleaved rotation, cache write
+    from nano_qwen3tts_vllm_b200.layers.rotary_embedding import PairRotary
+    rot = PairRotary(d // 2, 1e4, {"factor": 2.0}).to(dev)
+    u = torch.randn(n, H * d + 2 * G * d, device=dev).to(BF)
+    qo = torch.empty(n, H * d, dtype=BF, device=dev)
+    bq, bk = torch.zeros(H * d, device=dev), torch.zeros(G * d, device=dev)
+    ms = timed(lambda: nat.attn_prep(u, 0, H * d, H * d + G * d, bq, bk, bk, None, None, rot.freq, d // 2, play, qo, kc, vc, H, G, d, d, 1e-6,
+                                     interleaved=True))
+    res["attn_prep 8192 tokens (biases, pair rotation)"] = entry(ms, bytes_=n * (H * d * 2 + G * d * 4) * 2)
+    # ---- the in-and-out norms around a sublayer: dense, two branches, experts
+    x = torch.randn(n, D, device=dev)
+    a, b = torch.randn(n, D, device=dev).to(BF), torch.randn(n, D, device=dev).to(BF)
+    wv, g1 = torch.ones(D, device=dev), torch.ones(1, device=dev)
+    ms = timed(lambda: nat.sandwich_residual(x, g1, a=a, g_in=g1))
+    res["sandwich_residual 8192x2048 dense"] = entry(ms, bytes_=n * D * (4 * 2 + 2 + 2))
+    ms = timed(lambda: nat.sandwich_residual(x, g1, a=a, b=b, wa=wv, wb=wv, branch_scale=0.5, g_in=g1))
+    res["sandwich_residual 8192x2048 two branches"] = entry(ms, bytes_=n * D * (4 * 2 + 2 * 2 + 2))
+    z = torch.randn(n * 2, D, device=dev).to(BF)
+    zw = torch.rand(n, 2, device=dev)
+    zi = torch.randint(0, 17, (n, 2), device=dev, dtype=torch.int32)
+    ms = timed(lambda: nat.sandwich_residual(x, g1, z=z, zw=zw, z_idx=zi, n_real=16, hin=a, g_in=g1))
+    res["sandwich_residual 8192x2048 two experts of 16 + 1"] = entry(ms, bytes_=n * D * (4 * 2 + 3 * 2 + 2))
+    ffw = 9216
+    y = torch.randn(n, ffw, device=dev).to(BF)
+    coef = torch.tensor([1.0, 0.3, 0.1, 0.0], device=dev)
+    res["polynorm 8192x9216"] = entry(timed(lambda: nat.polynorm_(y, coef, 1e-6)), bytes_=n * ffw * 2 * 2)
+    # ---- gated linear attention: 8 heads of 128 x 128
+    Hr = H // 2
+    for name, ly, nn in (("prefill 4x2048", play, n), ("decode 64", layout(DECODE_SEQS, DECODE_CTX, 1, 1), DECODE_SEQS)):
+        uu = torch.randn(nn, 3 * Hr * d, device=dev).to(BF)
+        zz = torch.randn(nn, Hr * d, device=dev).to(BF)
+        st = torch.zeros(ly.n_seqs, Hr, d, d, device=dev)
+        oo = torch.empty(nn, Hr * d, device=dev)
+        bz = torch.zeros(Hr * d, device=dev)
+        ms = timed(lambda: nat.gated_linear_scan(uu[:, :Hr * d], uu[:, Hr * d:2 * Hr * d], uu[:, 2 * Hr * d:], zz, bz, 16.0, st, oo, ly, Hr, d, d),
+                   iters=3)
+        res[f"gated_linear_scan {name} (8 heads, 128 x 128)"] = entry(ms, bytes_=ly.n_seqs * Hr * d * d * 4 * 2 + nn * Hr * d * (4 * 2 + 4 + 4 * 2),
+                                                                     flops=nn * Hr * d * d * 6)
+    # ---- router: softmax over 17 outputs, correction, top 2
+    hh = torch.randn(n, D, device=dev).to(BF)
+    rw, rb = torch.randn(17, D, device=dev), torch.zeros(17, device=dev)
+    ti, tw = torch.empty(n, 2, dtype=torch.int32, device=dev), torch.empty(n, 2, device=dev)
+    off, sp = torch.empty(18, dtype=torch.int32, device=dev), torch.empty(n * 2, dtype=torch.int32, device=dev)
+    ms = timed(lambda: nat.moe_route(hh, rw, ti, tw, off, sp, 2, 1.0, bias=rb, mode=nat.ROUTE_SOFTMAX_ALL))
+    res["moe_route 8192 tokens, 16 + 1 outputs"] = entry(ms, bytes_=n * D * 2)
+    return res
+
+
+def main_teberax(device: str = "cuda:0") -> dict:
+    """``bench.py --lm-teberax``: Teberax beside Tibivik (the package's closest model: attention beside a recurrence behind
+    one projection, the same attention and recurrence kernels, over the same engine) at equal width, head layout and layer
+    count, then the kernels of both against their rooflines."""
+    import torch
+    t0 = time.time()
+    out = {"metric": "lm_prefill_decode_throughput", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights)",
+           "config": {"prefill": f"{PREFILL_SEQS}x{PREFILL_LEN} tokens per step", "decode": f"{DECODE_SEQS} sequences at context {DECODE_CTX}",
+                      "layers": LAYERS, "window": WINDOW, "page": PAGE}, "sizes": {}}
+    for name, s in SIZES.items():
+        row = {"teberax_moe16top2": bench_bokenex(s, True, device, "teberax"), "teberax_dense": bench_bokenex(s, False, device, "teberax"),
+               "tibivik": bench_bokenex(s, False, device, "tibivik")}
+        out["sizes"][name] = row
+        torch.cuda.empty_cache()
+    out["kernels"] = bench_teberax_kernels(device)
+    out["like_kernels"] = bench_hybrid_kernels(device)
+    out["seconds"] = round(time.time() - t0, 1)
+    return out
 
 
 def main_hybrid(device: str = "cuda:0") -> dict:

@@ -40,13 +40,39 @@ struct SandwichArgs {
   float eps;
 };
 
-template <typename T>
+// V consecutive columns of a row <-> floats; V = 4 needs 4-column alignment of the pointer (8 bytes of bf16, 16 of float)
+template <typename T, int V>
+__device__ __forceinline__ void ld_cols(const T* p, float* f) {
+  if constexpr (V == 1) {
+    f[0] = to_f(p[0]);
+  } else if constexpr (sizeof(T) == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  } else {
+    const uint2 r = ldg_v2(p);
+    f[0] = bf16lo(r.x); f[1] = bf16hi(r.x); f[2] = bf16lo(r.y); f[3] = bf16hi(r.y);
+  }
+}
+template <typename T, int V>
+__device__ __forceinline__ void st_cols(T* p, const float* f) {
+  if constexpr (V == 1) {
+    p[0] = from_f<T>(f[0]);
+  } else if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  } else {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
+  }
+}
+
+// One CTA per row; a thread owns groups of V consecutive columns (V = 4 when the row length and every pointer allow
+// vector accesses).  y is kept in shared memory between the passes; every sum of squares is a block sum in a fixed order.
+template <typename T, int V>
 __global__ void __launch_bounds__(SW_THREADS)
 sandwich_residual_kernel(const SandwichArgs p) {
-  extern __shared__ float ybuf[];                       // [cols]
+  extern __shared__ __align__(16) float ybuf[];         // [cols]
   __shared__ float red[33];
   const size_t r = blockIdx.x;
-  const int cols = p.cols;
+  const int cols = p.cols, step = blockDim.x * V, c0 = threadIdx.x * V;
   const float fc = static_cast<float>(cols);
   const T* a = static_cast<const T*>(p.a);
   if (a != nullptr) {
@@ -61,44 +87,77 @@ sandwich_residual_kernel(const SandwichArgs p) {
   if (p.wa != nullptr) {                                // two branches, each normed with its own weight vector
     const T* b = static_cast<const T*>(p.b) + r * cols;
     float sa = 0.f, sb = 0.f;
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-      const float va = to_f(a[c]), vb = to_f(b[c]);
-      sa += va * va; sb += vb * vb;
+    for (int c = c0; c < cols; c += step) {
+      float va[V], vb[V];
+      ld_cols<T, V>(a + c, va); ld_cols<T, V>(b + c, vb);
+#pragma unroll
+      for (int i = 0; i < V; ++i) { sa += va[i] * va[i]; sb += vb[i] * vb[i]; }
     }
     const float ia = 1.0f / sqrtf(block_sum(sa, red) / fc + p.eps);
     const float ib = 1.0f / sqrtf(block_sum(sb, red) / fc + p.eps);
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-      const float y = p.branch_scale * (to_f(a[c]) * ia * p.wa[c] + to_f(b[c]) * ib * p.wb[c]);
-      ybuf[c] = y;
-      ssq += y * y;
+    for (int c = c0; c < cols; c += step) {
+      float va[V], vb[V], wa[V], wb[V], y[V];
+      ld_cols<T, V>(a + c, va); ld_cols<T, V>(b + c, vb);
+      ld_cols<float, V>(p.wa + c, wa); ld_cols<float, V>(p.wb + c, wb);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        y[i] = p.branch_scale * (va[i] * ia * wa[i] + vb[i] * ib * wb[i]);
+        ssq += y[i] * y[i];
+      }
+      st_cols<float, V>(ybuf + c, y);
     }
   } else {
     const T* z = static_cast<const T*>(p.z);
     const T* hin = p.hin != nullptr ? static_cast<const T*>(p.hin) + r * cols : nullptr;
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-      float y = a != nullptr ? to_f(a[c]) : 0.f;
+    for (int c = c0; c < cols; c += step) {
+      float y[V];
+      if (a != nullptr) {
+        ld_cols<T, V>(a + c, y);
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) y[i] = 0.f;
+      }
       for (int k = 0; k < p.top; ++k) {                 // choices in ascending order: a fixed order of additions
         const size_t pr = r * p.top + k;
         const bool real = p.z_idx == nullptr || p.z_idx[pr] < p.n_real;
-        y += p.zw[pr] * (real ? to_f(z[pr * cols + c]) : to_f(hin[c]));
+        const float w = p.zw[pr];
+        float zv[V];
+        ld_cols<T, V>(real ? z + pr * cols + c : hin + c, zv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) y[i] += w * zv[i];
       }
-      ybuf[c] = y;
-      ssq += y * y;
+#pragma unroll
+      for (int i = 0; i < V; ++i) ssq += y[i] * y[i];
+      st_cols<float, V>(ybuf + c, y);
     }
   }
   const float inv = p.g_out[0] / sqrtf(block_sum(ssq, red) / fc + p.eps);
   float* xr = p.x + r * cols;
   float sx = 0.f;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    const float v = (p.init ? 0.f : xr[c]) + ybuf[c] * inv;
-    xr[c] = v;
-    ybuf[c] = v;
-    sx += v * v;
+  for (int c = c0; c < cols; c += step) {
+    float y[V], xv[V];
+    ld_cols<float, V>(ybuf + c, y);
+    if (p.init) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) xv[i] = 0.f;
+    } else {
+      ld_cols<float, V>(xr + c, xv);
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) { xv[i] += y[i] * inv; sx += xv[i] * xv[i]; }
+    st_cols<float, V>(xr + c, xv);
+    st_cols<float, V>(ybuf + c, xv);
   }
   if (p.h == nullptr) return;
   const float inv2 = p.g_in[0] / sqrtf(block_sum(sx, red) / fc + p.eps);
   T* hr = static_cast<T*>(p.h) + r * cols;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) hr[c] = from_f<T>(ybuf[c] * inv2);
+  for (int c = c0; c < cols; c += step) {
+    float xv[V];
+    ld_cols<float, V>(ybuf + c, xv);
+#pragma unroll
+    for (int i = 0; i < V; ++i) xv[i] *= inv2;
+    st_cols<T, V>(hr + c, xv);
+  }
 }
 
 // ------------------------------------------------------------------ PolyNorm, in place on the rows of y [rows, cols]
@@ -183,8 +242,19 @@ extern "C" int b2tts_sandwich_residual(float* x, const void* a, const int32_t* a
   SandwichArgs p{x, a, a_index, a_rows, b, wa, wb, branch_scale, z, zw, z_idx, top, n_real, hin, g_out, g_in, h, cols, init, eps};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t sm = static_cast<size_t>(cols) * sizeof(float);
-  if (dtype == B2TTS_DTYPE_BF16) sandwich_residual_kernel<__nv_bfloat16><<<rows, SW_THREADS, sm, st>>>(p);
-  else sandwich_residual_kernel<float><<<rows, SW_THREADS, sm, st>>>(p);
+  // vector accesses: rows of whole 4-column groups and every tensor 16-byte aligned (rows of `a`, `z`, `h` then start on
+  // 8-byte boundaries in bf16, 16-byte ones in float)
+  bool vec = cols % 4 == 0;
+  for (const void* q : {static_cast<const void*>(x), a, b, static_cast<const void*>(wa), static_cast<const void*>(wb), z, hin,
+                        static_cast<const void*>(h)})
+    vec = vec && (q == nullptr || aligned16(q));
+  if (dtype == B2TTS_DTYPE_BF16) {
+    if (vec) sandwich_residual_kernel<__nv_bfloat16, 4><<<rows, SW_THREADS, sm, st>>>(p);
+    else sandwich_residual_kernel<__nv_bfloat16, 1><<<rows, SW_THREADS, sm, st>>>(p);
+  } else {
+    if (vec) sandwich_residual_kernel<float, 4><<<rows, SW_THREADS, sm, st>>>(p);
+    else sandwich_residual_kernel<float, 1><<<rows, SW_THREADS, sm, st>>>(p);
+  }
   B2_CHECK_LAUNCH("sandwich_residual");
   return B2TTS_OK;
 }

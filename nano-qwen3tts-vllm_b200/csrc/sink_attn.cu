@@ -13,7 +13,7 @@
 // maps over one set of values).
 //
 // Three kernels share a launch: prompt portions in bf16 with head sizes 32..128 x 64, 128 run on the tensor cores
-// (sink_attn_mma_kernel), rows with ONE new token and a head size of 4, 8, 16 or 32 16-byte pieces (d = dv) in a kernel whose
+// (sink_attn_mma_kernel), rows with ONE new token and a head size of 4, 8, 16 or 32 16-byte pieces (dv = d or 2 d) in a kernel whose
 // lanes split a cached row (sink_attn_decode_kernel), everything else in the plain kernel; each skips the rows of the others.
 //
 // Plain kernel (bf16 or float, any head size up to 256): one CTA of four warps per token and 1, 2 or 4 query heads of one
@@ -272,18 +272,20 @@ static void launch_sink_plain_rep(int rep, cudaStream_t st, const void* q, const
 // (K and V pieces of four keys per lane group) are in flight before the first is used.  A score is the slice's dot product
 // summed over the LPK lanes by shuffles; every lane group keeps a running maximum and denominator per head (base 2), the
 // groups of a warp are merged by shuffles and the warps through shared memory, where the sink joins the denominator.
+// Values may be VR = 1 or 2 times as wide as keys (dv = VR * d): a lane then takes VR 16-byte pieces of a value row, LPK
+// pieces apart, so that the warp's loads stay contiguous.
 constexpr int SD_WARPS = 8, SD_AHEAD = 4;
 
-template <typename T, int LPK, int REP>
+template <typename T, int LPK, int REP, int VR>
 __global__ void __launch_bounds__(SD_WARPS * 32)
 sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
                         const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int64_t bt_stride,
                         const float* __restrict__ sink, const T* __restrict__ gate, int64_t ldg, int H, int G, int Gv, int page,
                         int mask_kind, int mask, int keep_first, float softcap, float scale) {
-  constexpr int N = Vec16<T>::N, D = LPK * N, KPW = 32 / LPK;
+  constexpr int N = Vec16<T>::N, D = LPK * N, DV = D * VR, KPW = 32 / LPK;
   constexpr float LOG2E = 1.4426950408889634f;
-  __shared__ float part[SD_WARPS][REP][D + 2];
+  __shared__ float part[SD_WARPS][REP][DV + 2];
   const int b = blockIdx.x;
   if (seq_len[b] != 1) return;
   const int h0 = blockIdx.y * REP, g = h0 / (H / G);
@@ -295,16 +297,18 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   if (mask > 0) lo = mask_kind == 0 ? max(0, i - mask + 1) : (i / mask) * mask;
   const int32_t* bt = block_tables + static_cast<int64_t>(b) * bt_stride;
   const size_t row = static_cast<size_t>(G) * D;          // elements of a cached key row
-  const size_t vrow = static_cast<size_t>(Gv) * D;        // and of a value row (dv = d)
+  const size_t vrow = static_cast<size_t>(Gv) * DV;       // and of a value row
   const int gv = g % Gv;
   const int npre = min(keep_first, lo), n_keys = npre + i - lo + 1;    // kept first keys the mask hides, then [lo, i]
   const float cap2 = softcap * LOG2E;                      // the cap in the base-2 domain the scores live in
-  float qv[REP][N], acc[REP][N], m[REP], l[REP];
+  float qv[REP][N], acc[REP][VR * N], m[REP], l[REP];
 #pragma unroll
   for (int r = 0; r < REP; ++r) {
     const T* qr = q + (t * H + h0 + r) * D + sub * N;
 #pragma unroll
-    for (int e = 0; e < N; ++e) { qv[r][e] = to_f(qr[e]) * (scale * LOG2E); acc[r][e] = 0.f; }
+    for (int e = 0; e < N; ++e) qv[r][e] = to_f(qr[e]) * (scale * LOG2E);
+#pragma unroll
+    for (int e = 0; e < VR * N; ++e) acc[r][e] = 0.f;
     m[r] = -1e30f; l[r] = 0.f;
   }
   auto unpack = [](const uint4& raw, float* f) {
@@ -317,19 +321,22 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   };
   constexpr int STEP = SD_WARPS * KPW;                     // keys the CTA takes per step
   for (int j0 = 0; j0 < n_keys; j0 += STEP * SD_AHEAD) {
-    uint4 kraw[SD_AHEAD], vraw[SD_AHEAD];
+    uint4 kraw[SD_AHEAD], vraw[SD_AHEAD][VR];
     bool ok[SD_AHEAD];
 #pragma unroll
     for (int u = 0; u < SD_AHEAD; ++u) {
       const int vi = j0 + u * STEP + warp * KPW + kg;
       const int j = vi < npre ? vi : lo + vi - npre;
       ok[u] = vi < n_keys;
-      kraw[u] = vraw[u] = make_uint4(0, 0, 0, 0);
+      kraw[u] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int p = 0; p < VR; ++p) vraw[u][p] = make_uint4(0, 0, 0, 0);
       if (ok[u]) {
         const int pg = j / page;
         const size_t slot = static_cast<size_t>(bt[pg]) * page + (j - pg * page);
         kraw[u] = ldg_v4(k_cache + slot * row + g * D + sub * N);
-        vraw[u] = ldg_v4(v_cache + slot * vrow + gv * D + sub * N);
+#pragma unroll
+        for (int p = 0; p < VR; ++p) vraw[u][p] = ldg_v4(v_cache + slot * vrow + gv * DV + (p * LPK + sub) * N);
       }
     }
     float sc[SD_AHEAD][REP];
@@ -358,19 +365,22 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
       m[r] = m_new;
       l[r] *= corr;
 #pragma unroll
-      for (int e = 0; e < N; ++e) acc[r][e] *= corr;
+      for (int e = 0; e < VR * N; ++e) acc[r][e] *= corr;
 #pragma unroll
       for (int u = 0; u < SD_AHEAD; ++u) sc[u][r] = exp2f(sc[u][r] - m_new);
     }
 #pragma unroll
     for (int u = 0; u < SD_AHEAD; ++u) {
-      float f[N];
-      unpack(vraw[u], f);
 #pragma unroll
-      for (int r = 0; r < REP; ++r) {
-        l[r] += sc[u][r];
+      for (int r = 0; r < REP; ++r) l[r] += sc[u][r];
 #pragma unroll
-        for (int e = 0; e < N; ++e) acc[r][e] += sc[u][r] * f[e];
+      for (int p = 0; p < VR; ++p) {
+        float f[N];
+        unpack(vraw[u][p], f);
+#pragma unroll
+        for (int r = 0; r < REP; ++r)
+#pragma unroll
+          for (int e = 0; e < N; ++e) acc[r][p * N + e] += sc[u][r] * f[e];
       }
     }
   }
@@ -384,7 +394,7 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
       const float ca = exp2f(m[r] - m_new), cb = exp2f(m_o - m_new);
       l[r] = l[r] * ca + l_o * cb;
 #pragma unroll
-      for (int e = 0; e < N; ++e) acc[r][e] = acc[r][e] * ca + __shfl_xor_sync(0xffffffffu, acc[r][e], o) * cb;
+      for (int e = 0; e < VR * N; ++e) acc[r][e] = acc[r][e] * ca + __shfl_xor_sync(0xffffffffu, acc[r][e], o) * cb;
       m[r] = m_new;
     }
   }
@@ -392,8 +402,10 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
 #pragma unroll
-      for (int e = 0; e < N; ++e) part[warp][r][sub * N + e] = acc[r][e];
-      if (sub == 0) { part[warp][r][D] = m[r]; part[warp][r][D + 1] = l[r]; }
+      for (int p = 0; p < VR; ++p)
+#pragma unroll
+        for (int e = 0; e < N; ++e) part[warp][r][(p * LPK + sub) * N + e] = acc[r][p * N + e];
+      if (sub == 0) { part[warp][r][DV] = m[r]; part[warp][r][DV + 1] = l[r]; }
     }
   }
   __syncthreads();
@@ -403,19 +415,19 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     float mm = sink != nullptr ? sink[h] * LOG2E : -1e30f;
     const float sk = mm;
 #pragma unroll
-    for (int w = 0; w < SD_WARPS; ++w) mm = fmaxf(mm, part[w][r][D]);
+    for (int w = 0; w < SD_WARPS; ++w) mm = fmaxf(mm, part[w][r][DV]);
     float den = sink != nullptr ? exp2f(sk - mm) : 0.f;
     float cw[SD_WARPS];
 #pragma unroll
     for (int w = 0; w < SD_WARPS; ++w) {
-      cw[w] = exp2f(part[w][r][D] - mm);
-      den += cw[w] * part[w][r][D + 1];
+      cw[w] = exp2f(part[w][r][DV] - mm);
+      den += cw[w] * part[w][r][DV + 1];
     }
     float gv = 1.f;
     if (gate != nullptr) gv = sigmoid_f(to_f(gate[t * ldg + h]));
     const float inv = gv / den;
-    T* orow = out + (t * H + h) * D;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    T* orow = out + (t * H + h) * DV;
+    for (int c = threadIdx.x; c < DV; c += blockDim.x) {
       float o = 0.f;
 #pragma unroll
       for (int w = 0; w < SD_WARPS; ++w) o += cw[w] * part[w][r][c];
@@ -424,34 +436,37 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   }
 }
 
-template <typename T, int LPK>
+template <typename T, int LPK, int VR>
 static void launch_sink_decode(int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
                                int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int Gv,
                                int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
-#define SD_GO(REP) sink_attn_decode_kernel<T, LPK, REP><<<dim3(n_seqs, H / REP), SD_WARPS * 32, 0, st>>>(static_cast<const T*>(q), \
+#define SD_GO(REP) sink_attn_decode_kernel<T, LPK, REP, VR><<<dim3(n_seqs, H / REP), SD_WARPS * 32, 0, st>>>(static_cast<const T*>(q), \
       static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, sink, \
       static_cast<const T*>(gate), ldg, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale)
-  if (rep % 4 == 0 && LPK * Vec16<T>::N <= 128) SD_GO(4);
-  else if (rep % 2 == 0) SD_GO(2);
+  if constexpr (LPK * Vec16<T>::N * VR <= 128) {          // four heads' accumulators fit registers and shared memory
+    if (rep % 4 == 0) { SD_GO(4); return; }
+  }
+  if (rep % 2 == 0) SD_GO(2);
   else SD_GO(1);
 #undef SD_GO
 }
 
-// the row-splitting kernel takes d = dv = LPK * (16 / sizeof(T)) with LPK in {4, 8, 16, 32}
+// the row-splitting kernel takes d = LPK * (16 / sizeof(T)) with LPK in {4, 8, 16, 32} and dv = d or 2 d
 template <typename T>
 static bool launch_sink_decode_any(int d, int dv, int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                    const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
                                    int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int Gv,
                                    int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
   constexpr int N = Vec16<T>::N;
-  if (d != dv || d % N != 0) return false;
+  if ((dv != d && dv != 2 * d) || d % N != 0) return false;
+  const bool wide = dv == 2 * d;
 #define SD_ARGS rep, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, n_seqs, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale
   switch (d / N) {
-    case 4: launch_sink_decode<T, 4>(SD_ARGS); return true;
-    case 8: launch_sink_decode<T, 8>(SD_ARGS); return true;
-    case 16: launch_sink_decode<T, 16>(SD_ARGS); return true;
-    case 32: launch_sink_decode<T, 32>(SD_ARGS); return true;
+    case 4: if (wide) launch_sink_decode<T, 4, 2>(SD_ARGS); else launch_sink_decode<T, 4, 1>(SD_ARGS); return true;
+    case 8: if (wide) launch_sink_decode<T, 8, 2>(SD_ARGS); else launch_sink_decode<T, 8, 1>(SD_ARGS); return true;
+    case 16: if (wide) launch_sink_decode<T, 16, 2>(SD_ARGS); else launch_sink_decode<T, 16, 1>(SD_ARGS); return true;
+    case 32: if (wide) launch_sink_decode<T, 32, 2>(SD_ARGS); else launch_sink_decode<T, 32, 1>(SD_ARGS); return true;
     default: return false;
   }
 #undef SD_ARGS
