@@ -286,9 +286,11 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   constexpr int N = Vec16<T>::N, D = LPK * N, DV = D * VR, KPW = 32 / LPK;
   constexpr float LOG2E = 1.4426950408889634f;
   __shared__ float part[SD_WARPS][REP][DV + 2];
-  const int b = blockIdx.x;
+  // the head groups of a sequence are neighbours in launch order: key heads that share a value head (v_heads < kv_heads)
+  // run at the same time and the second reader finds the value rows in L2
+  const int b = blockIdx.y;
   if (seq_len[b] != 1) return;
-  const int h0 = blockIdx.y * REP, g = h0 / (H / G);
+  const int h0 = blockIdx.x * REP, g = h0 / (H / G);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane % LPK, kg = lane / LPK;
   const size_t t = seq_start[b];
@@ -441,7 +443,7 @@ static void launch_sink_decode(int rep, cudaStream_t st, const void* q, const vo
                                const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
                                int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int Gv,
                                int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
-#define SD_GO(REP) sink_attn_decode_kernel<T, LPK, REP, VR><<<dim3(n_seqs, H / REP), SD_WARPS * 32, 0, st>>>(static_cast<const T*>(q), \
+#define SD_GO(REP) sink_attn_decode_kernel<T, LPK, REP, VR><<<dim3(H / REP, n_seqs), SD_WARPS * 32, 0, st>>>(static_cast<const T*>(q), \
       static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, sink, \
       static_cast<const T*>(gate), ldg, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale)
   if constexpr (LPK * Vec16<T>::N * VR <= 128) {          // four heads' accumulators fit registers and shared memory
