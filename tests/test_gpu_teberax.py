@@ -213,7 +213,7 @@ def _attn_case(nat, H, G, d, dv, page, seqs, *, window=0, keep_first=0, softcap=
 MIXED = [(0, 1), (0, 70), (3, 2), (64, 1), (40, 31), (129, 1), (65, 66)]
 
 
-@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 12, 12), (3, 1, 10, 6), (4, 1, 32, 64), (2, 2, 33, 200)])
+@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 12, 12), (3, 1, 10, 6), (8, 2, 32, 64), (2, 2, 33, 200)])
 @pytest.mark.parametrize("window,keep", [(0, 0), (1, 0), (7, 3), (64, 1), (65, 64), (20, 70), (200, 5)])
 def test_two_maps_over_shared_values_with_window_and_kept_first_keys(nat, H, G, d, dv, window, keep):
     out, ref = _attn_case(nat, H, G, d, dv, 16, MIXED, window=window, keep_first=keep, two_maps=True, seed=window + keep)
@@ -234,7 +234,7 @@ def test_capped_scores_and_a_zero_sink(nat, H, G, d, dv, softcap):
     assert rel(none, ref3) < 2e-5 and rel(none, ref) > 1e-3
 
 
-@pytest.mark.parametrize("H,G,d,dv,two", [(4, 1, 32, 64, True), (2, 1, 64, 64, True), (4, 2, 128, 128, False), (2, 2, 96, 64, False),
+@pytest.mark.parametrize("H,G,d,dv,two", [(8, 2, 32, 64, True), (2, 1, 64, 64, True), (4, 2, 128, 128, False), (2, 2, 96, 64, False),
                                           (3, 1, 48, 128, True)])
 @pytest.mark.parametrize("window,keep", [(0, 0), (1, 0), (7, 3), (64, 4), (65, 64), (20, 70), (130, 2)])
 def test_tensor_core_prompt_kernel_with_the_new_switches(nat, H, G, d, dv, two, window, keep):
@@ -444,7 +444,7 @@ CONFIGS = {
     "only_identity_experts_can_win": dict(moe=dict(router={"experts": 2, "identity": 4, "top": 2}), types=("attention", "latent_attention"),
                                           ff=("moe",)),
     "vector_width_shapes": dict(width=128, vocab=128, dense_ff=256,
-                                attention=dict(heads=4, kv_heads=1, dim=32, vdim=64, diff=0.2, scale=0.2, mask={"size": 40, "keep_first": 3}),
+                                attention=dict(heads=6, kv_heads=2, dim=32, vdim=64, diff=0.2, scale=0.2, mask={"size": 40, "keep_first": 3}),
                                 left=dict(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.15, softcap=20.0,
                                           rot={"dims": 16, "base": 1e4, "scaling": {"factor": 2.0}}),
                                 right=dict(heads=2, dim=32, vdim=64, tau=8.0, decay_rank=8),
