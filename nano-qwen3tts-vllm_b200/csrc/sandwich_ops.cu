@@ -162,24 +162,36 @@ sandwich_residual_kernel(const SandwichArgs p) {
 
 // ------------------------------------------------------------------ PolyNorm, in place on the rows of y [rows, cols]
 // y <- c0 N(y) + c1 N(y^2) + c2 N(y^3) + c3, powers element by element, N over the row.
-template <typename T>
+template <typename T, int V>
 __global__ void __launch_bounds__(SW_THREADS)
 polynorm_kernel(T* __restrict__ y, const float* __restrict__ coef, int cols, float eps) {
   __shared__ float red[33];
   T* yr = y + static_cast<size_t>(blockIdx.x) * cols;
+  const int step = blockDim.x * V, c0 = threadIdx.x * V;
   float s2 = 0.f, s4 = 0.f, s6 = 0.f;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    const float v = to_f(yr[c]), v2 = v * v;
-    s2 += v2; s4 += v2 * v2; s6 += v2 * v2 * v2;
+  for (int c = c0; c < cols; c += step) {
+    float v[V];
+    ld_cols<T, V>(yr + c, v);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float v2 = v[i] * v[i];
+      s2 += v2; s4 += v2 * v2; s6 += v2 * v2 * v2;
+    }
   }
   const float fc = static_cast<float>(cols);
   const float i1 = coef[0] / sqrtf(block_sum(s2, red) / fc + eps);
   const float i2 = coef[1] / sqrtf(block_sum(s4, red) / fc + eps);
   const float i3 = coef[2] / sqrtf(block_sum(s6, red) / fc + eps);
   const float c3 = coef[3];
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    const float v = to_f(yr[c]), v2 = v * v;
-    yr[c] = from_f<T>(v * i1 + v2 * i2 + v2 * v * i3 + c3);
+  for (int c = c0; c < cols; c += step) {
+    float v[V];
+    ld_cols<T, V>(yr + c, v);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float v2 = v[i] * v[i];
+      v[i] = v[i] * i1 + v2 * i2 + v2 * v[i] * i3 + c3;
+    }
+    st_cols<T, V>(yr + c, v);
   }
 }
 
@@ -265,8 +277,14 @@ extern "C" int b2tts_polynorm(void* y, const float* coef, int rows, int cols, fl
   if (rows == 0) return B2TTS_OK;
   B2_REQUIRE(y && coef, B2TTS_EINVAL, "polynorm: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == B2TTS_DTYPE_BF16) polynorm_kernel<__nv_bfloat16><<<rows, SW_THREADS, 0, st>>>(static_cast<__nv_bfloat16*>(y), coef, cols, eps);
-  else polynorm_kernel<float><<<rows, SW_THREADS, 0, st>>>(static_cast<float*>(y), coef, cols, eps);
+  const bool vec = cols % 4 == 0 && aligned16(y);
+  if (dtype == B2TTS_DTYPE_BF16) {
+    if (vec) polynorm_kernel<__nv_bfloat16, 4><<<rows, SW_THREADS, 0, st>>>(static_cast<__nv_bfloat16*>(y), coef, cols, eps);
+    else polynorm_kernel<__nv_bfloat16, 1><<<rows, SW_THREADS, 0, st>>>(static_cast<__nv_bfloat16*>(y), coef, cols, eps);
+  } else {
+    if (vec) polynorm_kernel<float, 4><<<rows, SW_THREADS, 0, st>>>(static_cast<float*>(y), coef, cols, eps);
+    else polynorm_kernel<float, 1><<<rows, SW_THREADS, 0, st>>>(static_cast<float*>(y), coef, cols, eps);
+  }
   B2_CHECK_LAUNCH("polynorm");
   return B2TTS_OK;
 }
