@@ -288,6 +288,64 @@ def test_far_key_among_hundreds_and_the_zero_sink_that_halves_a_head(nat, dtype)
     assert none[0].float().abs().max() > 1.9 * out[0].float().abs().max()     # one key: weight 1/2 with the sink, 1 without
 
 
+def _latent_case(nat, H, r, dr, window, page, seqs, dtype=torch.float32, spike=None, seed=0, path=0):
+    """Latent attention WITHOUT a sink: cached rows [c | kr] (kr stored turned), queries [absorbed | not yet turned]; the
+    plain model is multi-query softmax attention with key [c | kr] and value c.  ``spike`` = (sequence, key position)."""
+    from nano_qwen3tts_vllm_b200.layers.rotary_embedding import PairRotary
+    g = torch.Generator().manual_seed(seed)
+    base, scale = 50.0, 0.3
+    rot = PairRotary(dr, base, None).to(DEV)
+    nb = [(c + n + page - 1) // page for c, n in seqs]
+    perm = torch.randperm(sum(nb) + 3, generator=g).tolist()
+    cache = torch.zeros(sum(nb) + 3, page, r + dr, dtype=dtype, device=DEV)
+    flat = cache.view(-1, r + dr)
+    lay_seqs, QL, QR, refs, at = [], [], [], [], 0
+    for s, (c, n) in enumerate(seqs):
+        T = c + n
+        lat, kr = torch.randn(T, r, generator=g).to(dtype), torch.randn(T, dr, generator=g).to(dtype)
+        ql, qr = torch.randn(T, H, r, generator=g).to(dtype), torch.randn(T, H, dr, generator=g).to(dtype)
+        if spike is not None and spike[0] == s:
+            ql[:, :, 0] = 6.0                                   # every query looks along coordinate 0 ...
+            lat[:, 0] = 0.0
+            lat[spike[1], 0] = 40.0                             # ... where only the spiked key has anything
+            lat[spike[1], 1:] *= 5.0
+        bt = perm[at:at + nb[s]]
+        at += nb[s]
+        slots = torch.tensor([bt[p // page] * page + p % page for p in range(T)])
+        flat[slots.to(DEV)] = torch.cat([lat, kr], 1).to(DEV)
+        q = torch.cat([ql.double(), O.rotate_pairs(qr.double(), torch.arange(T), dr, base)], -1)
+        k = torch.cat([lat.double(), kr.double()], -1)[:, None, :]
+        refs.append(O.softmax_attention(q, k, lat.double()[:, None, :], scale, O.visible(T, window or None))[c:])
+        lay_seqs.append((c, n, 0, bt)), QL.append(ql[c:]), QR.append(qr[c:])
+    lay = Lay(lay_seqs, page, max(nb))
+    n_new = lay.n_tokens
+    ql = torch.cat(QL).transpose(0, 1).contiguous().to(DEV)                  # [H, n, r]
+    qr = torch.cat(QR).contiguous().to(DEV)                                  # [n, H, dr]
+    out = torch.full((H, n_new, r), 7.0, dtype=dtype, device=DEV)
+    nat.latent_attn(ql, (r, n_new * r), qr, (H * dr, dr), cache, out, (r, n_new * r), None, rot.freq, 1.0, dr, lay, H, r, dr, page, window,
+                    scale, path)
+    return rel(out.transpose(0, 1), torch.cat(refs))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,r,dr", [(3, 24, 6), (4, 32, 16), (16, 128, 32)])
+def test_latent_attention_without_a_sink_at_window_edges_page_borders_and_far_back(nat, dtype, H, r, dr):
+    tol = TOL[dtype]
+    for window in (0, 1, 7, 65):
+        assert _latent_case(nat, H, r, dr, window, 16, [(0, 1), (0, 70), (3, 2), (64, 1), (40, 31), (129, 1)], dtype=dtype, seed=window) < tol
+    page, window = 16, 33
+    for p in (page - 1, page, 2 * page + 5):                    # the spiked key is seen by queries p .. p + window - 1 only
+        seqs = [(p + window - 3, 6), (p + window - 1, 1), (p + window, 1), (p, 1), (0, p + 2)]
+        for sp in range(len(seqs)):
+            assert _latent_case(nat, H, r, dr, window, page, seqs, dtype=dtype, spike=(sp, p), seed=p) < tol, (p, sp)
+    for window, back in [(0, 699), (600, 599), (600, 600)]:
+        assert _latent_case(nat, H, r, dr, window, 64, [(700, 1), (680, 21)], dtype=dtype, spike=(0, 700 - back), seed=back) < tol
+        assert _latent_case(nat, H, r, dr, window, 64, [(700, 1), (680, 21)], dtype=dtype, spike=(1, 700 - back), seed=back) < tol
+    if dtype == torch.bfloat16 and r % 32 == 0:                 # the tensor-core kernel against the plain one
+        a = _latent_case(nat, H, r, dr, 65, 16, [(0, 150), (64, 70), (129, 1)], dtype=dtype, seed=5, path=nat.LATENT_ATTN_PLAIN)
+        assert a < tol
+
+
 # ------------------------------------------------------------------------------------------------ recurrence, router
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,d,dv", [(2, 5, 7), (3, 32, 32), (1, 40, 100), (2, 130, 16)])
