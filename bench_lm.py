@@ -677,7 +677,7 @@ def bench_teberax_kernels(device: str) -> dict:
 
     def diff(lay):
         q = torch.randn(lay.n_tokens, 2 * H * dq, device=dev).to(BF)
-        maps = torch.empty(lay.n_tokens, 2 * H * d, dtype=BF, device=dev)
+        maps = torch.empty(lay.n_tokens, 2 * H * d, dtype=torch.float32, device=dev)     # unrounded, as the model asks for them
         return maps, (lambda: nat.sink_attn(q, kc2, vc, maps, lay, None, None, 2 * H, 2 * G, dq, d, PAGE, nat.MASK_WINDOW, WINDOW, dq ** -0.5,
                                             v_heads=G, keep_first=4))
 
@@ -688,7 +688,7 @@ def bench_teberax_kernels(device: str) -> dict:
     res["sink_attn prefill 4x2048 two maps, window 1024 + 4 kept"] = entry(timed(fn, iters=3), flops=pairs_w * 2 * H * 2 * (dq + d))
     oc = torch.empty(n, H * d, dtype=BF, device=dev)
     res["diff_combine 8192 tokens x 16 heads x 128"] = entry(timed(lambda: nat.diff_combine(maps, oc, 0.3, 0.5, H, d, 1e-6)),
-                                                            bytes_=n * H * d * 3 * 2)
+                                                            bytes_=n * H * d * (2 * 4 + 2))
     # ---- attention preparation: biases, interleaved rotation, cache write
     from nano_qwen3tts_vllm_b200.layers.rotary_embedding import PairRotary
     rot = PairRotary(d // 2, 1e4, {"factor": 2.0}).to(dev)

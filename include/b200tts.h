@@ -553,7 +553,8 @@ B2TTS_API int b2tts_attn_prep(const void* u, int64_t ldu, int q_off, int k_off, 
  * included.  Token i sees key j <= i with j >= max(0, i - mask + 1) (mask_kind 0, a sliding window) or j >= floor(i / mask) *
  * mask (mask_kind 1, chunks counted from position 0); mask <= 0: every j <= i.  keep_first F > 0: keys j < F stay visible
  * behind the mask.  softcap c > 0: a scaled score s becomes c tanh(s / c).  v_heads: value heads in v_cache, key head g reads
- * value head g mod v_heads (v_heads == kv_heads: one each).  gate (optional): element (t, h) at
+ * value head g mod v_heads (v_heads == kv_heads: one each).  out_f32 != 0 with bf16 inputs: out is a float tensor (results not
+ * rounded to 16 bits).  gate (optional): element (t, h) at
  * gate[t * ldg + h]; the head's output is multiplied by its sigmoid.  q [n, heads*dim], out [n, heads*vdim].  max_new >= every
  * seq_len[b].  path 0 = choose (bf16 prompt portions with head sizes the tensor-core kernel is built for run there, everything
  * else in the plain kernel), 1 = the plain kernel, 2 = the tensor-core kernel for prompt portions (fails if the sizes do not fit). */
@@ -562,7 +563,7 @@ B2TTS_API int b2tts_sink_attn(const void* q, const void* k_cache, const void* v_
                               const int32_t* block_tables, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg,
                               int n_tokens, int n_seqs, int max_new, int heads, int kv_heads, int v_heads, int dim, int vdim,
                               int page, int mask_kind, int mask, int keep_first, float softcap, float scale, int dtype, int path,
-                              void* stream);
+                              int out_f32, void* stream);
 /* out[t, c] = act(bias[c] + sum_j w[c, j] * u(position(t) - taps + 1 + j)[c_off + c]) for c < channels (act 0: none, 1: SiLU;
  * bias may be null).  Earlier positions come from this step's rows, from state [slots, taps-1, channels] (the sequence's last
  * rows, oldest first, advanced by this call) or are zero before position 0.  max_new >= every seq_len[b] (0: unknown). */
@@ -620,9 +621,10 @@ B2TTS_API int b2tts_sandwich_residual(float* x, const void* a, const int32_t* a_
                                       int rows, int cols, int init, float eps, int dtype, void* stream);
 /* In place on rows of y: coef[0] N(y) + coef[1] N(y^2) + coef[2] N(y^3) + coef[3], powers element by element. */
 B2TTS_API int b2tts_polynorm(void* y, const float* coef, int rows, int cols, float eps, int dtype, void* stream);
-/* maps [rows, 2, heads, vdim]: out[r, h] = (maps[r, 0, h] - lambda * maps[r, 1, h]) / sqrt(mean over vdim of its square + eps) * mult. */
+/* maps [rows, 2, heads, vdim]: out[r, h] = (maps[r, 0, h] - lambda * maps[r, 1, h]) / sqrt(mean over vdim of its square + eps) * mult.
+ * maps_f32 != 0: the maps are floats whatever `dtype` (the type of out) is. */
 B2TTS_API int b2tts_diff_combine(const void* maps, void* out, float lambda, float mult, int rows, int heads, int vdim, float eps,
-                                 int dtype, void* stream);
+                                 int maps_f32, int dtype, void* stream);
 /* In place: y <- cap * tanh(y / cap). */
 B2TTS_API int b2tts_tanh_cap(float* y, int64_t n, float cap, void* stream);
 

@@ -102,11 +102,11 @@ def _load():
         "b2tts_stream_mix_norm": (I, [P, P, P, F, F, P, P, P, P, P, I, I, I, F, I, P]),
         "b2tts_stream_gather_norm": (I, [P, P, P, P, P, I, I, I, F, I, P]),
         "b2tts_attn_prep": (I, [P, L, I, I, I, P, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, F, I, I, I, P]),
-        "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, I, I, I, I, F, F, I, I, P]),
+        "b2tts_sink_attn": (I, [P, P, P, P, P, P, P, P, P, P, L, P, P, L, I, I, I, I, I, I, I, I, I, I, I, I, F, F, I, I, I, P]),
         "b2tts_gated_linear_scan": (I, [P, L, P, L, P, L, P, L, P, F, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
         "b2tts_sandwich_residual": (I, [P, P, P, I, P, P, P, F, P, P, P, I, I, P, P, P, P, I, I, I, F, I, P]),
         "b2tts_polynorm": (I, [P, P, I, I, F, I, P]),
-        "b2tts_diff_combine": (I, [P, P, F, F, I, I, I, F, I, P]),
+        "b2tts_diff_combine": (I, [P, P, F, F, I, I, I, F, I, I, P]),
         "b2tts_tanh_cap": (I, [P, L, F, P]),
         "b2tts_short_conv_act": (I, [P, L, I, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, I, P]),
         "b2tts_gated_group_norm": (I, [P, P, L, P, I, I, I, I, F, P, I, I, I, P]),
@@ -976,16 +976,17 @@ def sink_attn(q, k_cache, v_cache, out, lay, sink, gate, heads, kv_heads, dim, v
               v_heads=None, keep_first=0, softcap=0.0):
     """``gate``: a column slice [n, heads] of the merged projection (or None).  ``sink`` None: an ordinary softmax.
     ``v_heads``: value heads in the cache (key head g reads value head g mod v_heads; default ``kv_heads``);
-    ``keep_first``: keys below this position stay visible behind the mask; ``softcap`` c > 0: scores become c tanh(s / c)."""
+    ``keep_first``: keys below this position stay visible behind the mask; ``softcap`` c > 0: scores become c tanh(s / c).
+    ``out`` may be a float tensor beside bfloat16 inputs: the results are then not rounded to 16 bits."""
     dt = _act(q, "q")
-    assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype and out.is_contiguous()
+    assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype in (q.dtype, F32) and out.is_contiguous()
     assert gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1)
     _check(_load().b2tts_sink_attn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), lay.tok_seq.data_ptr(),
                                    lay.positions.data_ptr(), lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(),
                                    lay.block_tables.data_ptr(), lay.block_tables.stride(0), _ptr(sink), _ptr(gate),
                                    0 if gate is None else gate.stride(0), lay.n_tokens, lay.n_seqs, lay.max_new, heads, kv_heads,
                                    kv_heads if v_heads is None else v_heads, dim, vdim, page, mask_kind, mask, keep_first, softcap,
-                                   scale, dt, path, _stream()), "sink_attn")
+                                   scale, dt, path, int(out.dtype == F32 and q.dtype != F32), _stream()), "sink_attn")
 
 
 def short_conv_act(u, c_off, channels, w, bias, state, lay, out, taps, act=1):
@@ -1091,12 +1092,13 @@ def polynorm_(y, coef, eps):
 
 
 def diff_combine(maps, out, lam, mult, heads, vdim, eps):
-    """maps [n, 2 * heads * vdim] (first map's heads, then the second's) -> out [n, heads * vdim] =
+    """maps [n, 2 * heads * vdim] (first map's heads, then the second's; floats or of out's type) -> out [n, heads * vdim] =
     head_rms_norm(map1 - lam * map2) * mult."""
-    dt = _act(maps, "maps")
-    assert out.dtype == maps.dtype and maps.is_contiguous() and out.is_contiguous()
-    _check(_load().b2tts_diff_combine(maps.data_ptr(), out.data_ptr(), lam, mult, maps.shape[0], heads, vdim, eps, dt, _stream()),
-           "diff_combine")
+    dt = _act(out, "out")
+    _cuda(maps, None, "maps")
+    assert maps.dtype in (out.dtype, F32) and maps.is_contiguous()
+    _check(_load().b2tts_diff_combine(maps.data_ptr(), out.data_ptr(), lam, mult, maps.shape[0], heads, vdim, eps,
+                                      int(maps.dtype == F32 and out.dtype != F32), dt, _stream()), "diff_combine")
     return out
 
 

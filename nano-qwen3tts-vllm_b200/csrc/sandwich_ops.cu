@@ -197,19 +197,20 @@ polynorm_kernel(T* __restrict__ y, const float* __restrict__ coef, int cols, flo
 
 // ------------------------------------------------------------------ two attention maps over the same values -> one output
 // maps [rows, 2, H, dv] (the first map's heads, then the second map's); out[r, h] = N_head(maps[r, 0, h] - lambda * maps[r, 1, h])
-// * mult, N over the head's dv values without a weight.  One warp per (row, head).
+// * mult, N over the head's dv values without a weight.  One warp per (row, head).  The maps may be floats while the output
+// has the activation type, so that the difference is taken before anything is rounded to 16 bits.
 constexpr int DC_PER_LANE = 8;                          // value sizes up to 256
 
-template <typename T>
+template <typename TI, typename T>
 __global__ void __launch_bounds__(128)
-diff_combine_kernel(const T* __restrict__ maps, T* __restrict__ out, float lambda, float mult, int rows, int H, int dv, float eps) {
+diff_combine_kernel(const TI* __restrict__ maps, T* __restrict__ out, float lambda, float mult, int rows, int H, int dv, float eps) {
   const int lane = threadIdx.x & 31;
   const size_t w = static_cast<size_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= static_cast<size_t>(rows) * H) return;
   const size_t r = w / H;
   const int h = static_cast<int>(w % H);
-  const T* m1 = maps + (r * 2 * H + h) * dv;
-  const T* m2 = m1 + static_cast<size_t>(H) * dv;
+  const TI* m1 = maps + (r * 2 * H + h) * dv;
+  const TI* m2 = m1 + static_cast<size_t>(H) * dv;
   float o[DC_PER_LANE], ss = 0.f;
 #pragma unroll
   for (int i = 0; i < DC_PER_LANE; ++i) {
@@ -290,7 +291,7 @@ extern "C" int b2tts_polynorm(void* y, const float* coef, int rows, int cols, fl
 }
 
 extern "C" int b2tts_diff_combine(const void* maps, void* out, float lambda, float mult, int rows, int heads, int vdim, float eps,
-                                  int dtype, void* stream) {
+                                  int maps_f32, int dtype, void* stream) {
   B2_REQUIRE(rows >= 0 && heads > 0 && vdim > 0, B2TTS_EINVAL, "diff_combine: rows=%d heads=%d vdim=%d", rows, heads, vdim);
   B2_REQUIRE(vdim <= 32 * DC_PER_LANE, B2TTS_EUNSUPPORTED, "diff_combine: value size %d above %d", vdim, 32 * DC_PER_LANE);
   B2_REQUIRE(B2_ROW_DTYPE_OK(dtype), B2TTS_EINVAL, "diff_combine: dtype %d", dtype);
@@ -299,12 +300,15 @@ extern "C" int b2tts_diff_combine(const void* maps, void* out, float lambda, flo
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t warps = static_cast<size_t>(rows) * heads;
   const unsigned blocks = static_cast<unsigned>((warps + 3) / 4);
-  if (dtype == B2TTS_DTYPE_BF16)
-    diff_combine_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(maps), static_cast<__nv_bfloat16*>(out),
-                                                               lambda, mult, rows, heads, vdim, eps);
+  if (dtype == B2TTS_DTYPE_BF16 && maps_f32)
+    diff_combine_kernel<float, __nv_bfloat16><<<blocks, 128, 0, st>>>(static_cast<const float*>(maps), static_cast<__nv_bfloat16*>(out),
+                                                                      lambda, mult, rows, heads, vdim, eps);
+  else if (dtype == B2TTS_DTYPE_BF16)
+    diff_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(maps),
+                                                                              static_cast<__nv_bfloat16*>(out), lambda, mult, rows, heads, vdim, eps);
   else
-    diff_combine_kernel<float><<<blocks, 128, 0, st>>>(static_cast<const float*>(maps), static_cast<float*>(out), lambda, mult, rows, heads,
-                                                       vdim, eps);
+    diff_combine_kernel<float, float><<<blocks, 128, 0, st>>>(static_cast<const float*>(maps), static_cast<float*>(out), lambda, mult, rows,
+                                                              heads, vdim, eps);
   B2_CHECK_LAUNCH("diff_combine");
   return B2TTS_OK;
 }

@@ -32,6 +32,13 @@ constexpr int SA_WARPS = 4;
 constexpr int SA_MAX_PER_LANE = 8;        // value sizes up to 256
 constexpr int SA_ROWS_AHEAD = 8;          // value rows in flight per lane
 
+// an output element: of the activation type, or a float where the caller asked for unrounded results (`f32`)
+template <typename T>
+__device__ __forceinline__ void put_out(T* out, size_t idx, float v, int f32) {
+  if (f32) reinterpret_cast<float*>(out)[idx] = v;
+  else out[idx] = from_f<T>(v);
+}
+
 template <typename T> struct Vec16;       // how many T fit 16 bytes
 template <> struct Vec16<float> { static constexpr int N = 4; };
 template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
@@ -111,7 +118,7 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_len,
                  const int32_t* __restrict__ block_tables, int64_t bt_stride, const float* __restrict__ sink,
                  const T* __restrict__ gate, int64_t ldg, int H, int G, int Gv, int d, int dv, int page, int mask_kind, int mask,
-                 int keep_first, float softcap, float scale, int only_single) {
+                 int keep_first, float softcap, float scale, int only_single, int out_f32) {
   extern __shared__ float smem[];
   const int qstride = (d + 3) & ~3;
   float* qs = smem;                                   // [REP][qstride]
@@ -120,11 +127,11 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
   const int h0 = blockIdx.y * REP, g = h0 / (H / G);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int b = tok_seq[t];
-  T* orow = out + (t * H + h0) * dv;                  // the REP heads' outputs are adjacent
+  const size_t obase = (t * H + h0) * dv;             // the REP heads' outputs are adjacent
   if ((only_single & 1) && seq_len[b] > 1) return;    // the tensor-core kernel owns prompt portions
   if ((only_single & 2) && seq_len[b] == 1) return;   // the row-splitting kernel owns one-token rows
   if (seq_len[b] <= 0) {                              // padding row
-    for (int c = threadIdx.x; c < REP * dv; c += blockDim.x) orow[c] = from_f<T>(0.f);
+    for (int c = threadIdx.x; c < REP * dv; c += blockDim.x) put_out(out, obase + c, 0.f, out_f32);
     return;
   }
   const int i = positions[t];
@@ -235,7 +242,7 @@ sink_attn_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
       float o = 0.f;
 #pragma unroll
       for (int w = 0; w < SA_WARPS; ++w) o += cw[w] * part[(w * REP + r) * pstride + c];
-      orow[r * dv + c] = from_f<T>(o * inv);
+      put_out(out, obase + r * dv + c, o * inv, out_f32);
     }
   }
 }
@@ -244,11 +251,11 @@ template <typename T, int REP>
 static void launch_sink_plain(cudaStream_t st, const void* q, const void* kc, const void* vc, void* out, const int32_t* tok_seq,
                               const int32_t* positions, const int32_t* seq_len, const int32_t* bt, int64_t bt_stride, const float* sink,
                               const void* gate, int64_t ldg, int n_tokens, int H, int G, int Gv, int d, int dv, int page, int mask_kind,
-                              int mask, int keep_first, float softcap, float scale, int only_single) {
+                              int mask, int keep_first, float softcap, float scale, int only_single, int out_f32) {
   const size_t sm = (static_cast<size_t>(REP) * ((d + 3) & ~3) + static_cast<size_t>(SA_WARPS) * REP * (dv + 2)) * sizeof(float);
   sink_attn_kernel<T, REP><<<dim3(n_tokens, H / REP), SA_WARPS * 32, sm, st>>>(
       static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), tok_seq, positions, seq_len, bt,
-      bt_stride, sink, static_cast<const T*>(gate), ldg, H, G, Gv, d, dv, page, mask_kind, mask, keep_first, softcap, scale, only_single);
+      bt_stride, sink, static_cast<const T*>(gate), ldg, H, G, Gv, d, dv, page, mask_kind, mask, keep_first, softcap, scale, only_single, out_f32);
 }
 
 template <typename T>
@@ -256,8 +263,8 @@ static void launch_sink_plain_rep(int rep, cudaStream_t st, const void* q, const
                                   const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_len, const int32_t* bt,
                                   int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_tokens, int H, int G, int Gv,
                                   int d, int dv, int page, int mask_kind, int mask, int keep_first, float softcap, float scale,
-                                  int only_single) {
-#define SINK_PLAIN_ARGS st, q, kc, vc, out, tok_seq, positions, seq_len, bt, bt_stride, sink, gate, ldg, n_tokens, H, G, Gv, d, dv, page, mask_kind, mask, keep_first, softcap, scale, only_single
+                                  int only_single, int out_f32) {
+#define SINK_PLAIN_ARGS st, q, kc, vc, out, tok_seq, positions, seq_len, bt, bt_stride, sink, gate, ldg, n_tokens, H, G, Gv, d, dv, page, mask_kind, mask, keep_first, softcap, scale, only_single, out_f32
   // heads of a group that share a CTA: as many as divide the group, up to four (two for wide values: registers)
   if (rep % 4 == 0 && dv <= 128) launch_sink_plain<T, 4>(SINK_PLAIN_ARGS);
   else if (rep % 2 == 0) launch_sink_plain<T, 2>(SINK_PLAIN_ARGS);
@@ -282,7 +289,7 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int64_t bt_stride,
                         const float* __restrict__ sink, const T* __restrict__ gate, int64_t ldg, int H, int G, int Gv, int page,
-                        int mask_kind, int mask, int keep_first, float softcap, float scale) {
+                        int mask_kind, int mask, int keep_first, float softcap, float scale, int out_f32) {
   constexpr int N = Vec16<T>::N, D = LPK * N, DV = D * VR, KPW = 32 / LPK;
   constexpr float LOG2E = 1.4426950408889634f;
   __shared__ float part[SD_WARPS][REP][DV + 2];
@@ -428,12 +435,12 @@ sink_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     float gv = 1.f;
     if (gate != nullptr) gv = sigmoid_f(to_f(gate[t * ldg + h]));
     const float inv = gv / den;
-    T* orow = out + (t * H + h) * DV;
+    const size_t obase = (t * H + h) * DV;
     for (int c = threadIdx.x; c < DV; c += blockDim.x) {
       float o = 0.f;
 #pragma unroll
       for (int w = 0; w < SD_WARPS; ++w) o += cw[w] * part[w][r][c];
-      orow[c] = from_f<T>(o * inv);
+      put_out(out, obase + c, o * inv, out_f32);
     }
   }
 }
@@ -442,10 +449,10 @@ template <typename T, int LPK, int VR>
 static void launch_sink_decode(int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
                                int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int Gv,
-                               int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
+                               int page, int mask_kind, int mask, int keep_first, float softcap, float scale, int out_f32) {
 #define SD_GO(REP) sink_attn_decode_kernel<T, LPK, REP, VR><<<dim3(H / REP, n_seqs), SD_WARPS * 32, 0, st>>>(static_cast<const T*>(q), \
       static_cast<const T*>(kc), static_cast<const T*>(vc), static_cast<T*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, sink, \
-      static_cast<const T*>(gate), ldg, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale)
+      static_cast<const T*>(gate), ldg, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale, out_f32)
   if constexpr (LPK * Vec16<T>::N * VR <= 128) {          // four heads' accumulators fit registers and shared memory
     if (rep % 4 == 0) { SD_GO(4); return; }
   }
@@ -459,11 +466,11 @@ template <typename T>
 static bool launch_sink_decode_any(int d, int dv, int rep, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                    const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
                                    int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int n_seqs, int H, int G, int Gv,
-                                   int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
+                                   int page, int mask_kind, int mask, int keep_first, float softcap, float scale, int out_f32) {
   constexpr int N = Vec16<T>::N;
   if ((dv != d && dv != 2 * d) || d % N != 0) return false;
   const bool wide = dv == 2 * d;
-#define SD_ARGS rep, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, n_seqs, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale
+#define SD_ARGS rep, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, n_seqs, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale, out_f32
   switch (d / N) {
     case 4: if (wide) launch_sink_decode<T, 4, 2>(SD_ARGS); else launch_sink_decode<T, 4, 1>(SD_ARGS); return true;
     case 8: if (wide) launch_sink_decode<T, 8, 2>(SD_ARGS); else launch_sink_decode<T, 8, 1>(SD_ARGS); return true;
@@ -508,7 +515,7 @@ sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                      const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int64_t bt_stride,
                      const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int64_t ldg, int H, int G, int Gv,
-                     int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
+                     int page, int mask_kind, int mask, int keep_first, float softcap, float scale, int out_f32) {
   constexpr int QS = D + 8, VS = DV + 8;             // padded rows: 16-byte aligned, ldmatrix rows land in distinct banks
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char sm_raw[];
@@ -671,10 +678,18 @@ sink_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     const size_t row = static_cast<size_t>(start + t0 + row_lo + 8 * half);
     float inv = 1.0f / (half ? l1 : l0);
     if (gate != nullptr) inv *= sigmoid_f(__bfloat162float(gate[row * ldg + h]));
-    __nv_bfloat16* o = out + (row * H + h) * DV + 2 * (lane & 3);
+    const size_t obase = (row * H + h) * DV + 2 * (lane & 3);
+    if (out_f32) {
+      float* o = reinterpret_cast<float*>(out) + obase;
 #pragma unroll
-    for (int nt = 0; nt < DV / 8; ++nt)
-      *reinterpret_cast<uint32_t*>(o + nt * 8) = pack_bf16(oacc[nt][2 * half] * inv, oacc[nt][2 * half + 1] * inv);
+      for (int nt = 0; nt < DV / 8; ++nt)
+        *reinterpret_cast<float2*>(o + nt * 8) = make_float2(oacc[nt][2 * half] * inv, oacc[nt][2 * half + 1] * inv);
+    } else {
+      __nv_bfloat16* o = out + obase;
+#pragma unroll
+      for (int nt = 0; nt < DV / 8; ++nt)
+        *reinterpret_cast<uint32_t*>(o + nt * 8) = pack_bf16(oacc[nt][2 * half] * inv, oacc[nt][2 * half + 1] * inv);
+    }
   }
 }
 
@@ -682,7 +697,7 @@ template <int D, int DV>
 static cudaError_t launch_sink_mma(int max_new, int n_seqs, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                    const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
                                    int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int H, int G, int Gv, int page,
-                                   int mask_kind, int mask, int keep_first, float softcap, float scale) {
+                                   int mask_kind, int mask, int keep_first, float softcap, float scale, int out_f32) {
   auto kern = sink_attn_mma_kernel<D, DV>;
   const size_t smem = sizeof(__nv_bfloat16) * ((SM_BM + 2 * SM_BN) * (D + 8) + 2 * SM_BN * (DV + 8));
   static bool opted = false;
@@ -695,7 +710,7 @@ static cudaError_t launch_sink_mma(int max_new, int n_seqs, cudaStream_t st, con
   const dim3 grid((max_new + SM_BM - 1) / SM_BM, H, n_seqs);
   kern<<<grid, 128, smem, st>>>(static_cast<const B*>(q), static_cast<const B*>(kc), static_cast<const B*>(vc), static_cast<B*>(out),
                                 seq_start, seq_pos0, seq_len, bt, bt_stride, sink, static_cast<const B*>(gate), ldg, H, G, Gv, page,
-                                mask_kind, mask, keep_first, softcap, scale);
+                                mask_kind, mask, keep_first, softcap, scale, out_f32);
   return cudaSuccess;
 }
 
@@ -704,12 +719,13 @@ static bool sink_mma_shape(int d, int dv) {
   return (d == 32 || d == 48 || d == 64 || d == 96 || d == 128) && (dv == 64 || dv == 128);
 }
 
-#define SINK_MMA_ARGS max_new, n_seqs, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale
+#define SINK_MMA_ARGS max_new, n_seqs, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, sink, gate, ldg, H, G, Gv, page, mask_kind, mask, keep_first, softcap, scale, out_f32
 template <int D>
 static cudaError_t launch_sink_mma_dv(int dv, int max_new, int n_seqs, cudaStream_t st, const void* q, const void* kc, const void* vc,
                                       void* out, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
                                       const int32_t* bt, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg, int H,
-                                      int G, int Gv, int page, int mask_kind, int mask, int keep_first, float softcap, float scale) {
+                                      int G, int Gv, int page, int mask_kind, int mask, int keep_first, float softcap, float scale,
+                                      int out_f32) {
   return dv == 64 ? launch_sink_mma<D, 64>(SINK_MMA_ARGS) : launch_sink_mma<D, 128>(SINK_MMA_ARGS);
 }
 
@@ -723,7 +739,9 @@ extern "C" int b2tts_sink_attn(const void* q, const void* k_cache, const void* v
                                const int32_t* positions, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
                                const int32_t* block_tables, int64_t bt_stride, const float* sink, const void* gate, int64_t ldg,
                                int n_tokens, int n_seqs, int max_new, int heads, int kv_heads, int v_heads, int dim, int vdim, int page,
-                               int mask_kind, int mask, int keep_first, float softcap, float scale, int dtype, int path, void* stream) {
+                               int mask_kind, int mask, int keep_first, float softcap, float scale, int dtype, int path, int out_f32,
+                               void* stream) {
+  if (dtype == B2TTS_DTYPE_F32) out_f32 = 0;         // the outputs are floats already
   B2_REQUIRE(v_heads > 0 && kv_heads % v_heads == 0 && keep_first >= 0 && softcap >= 0.f, B2TTS_EINVAL,
              "sink_attn: bad switches (v_heads=%d of kv_heads=%d, keep_first=%d, softcap=%g)", v_heads, kv_heads, keep_first, softcap);
   if (mask <= 0) keep_first = 0;                     // nothing is hidden, nothing to keep
@@ -762,22 +780,22 @@ extern "C" int b2tts_sink_attn(const void* q, const void* k_cache, const void* v
     if (dtype == B2TTS_DTYPE_BF16)
       split = launch_sink_decode_any<__nv_bfloat16>(dim, vdim, heads / kv_heads, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
                                                     block_tables, bt_stride, sink, gate, ldg, n_seqs, heads, kv_heads, v_heads, page, mask_kind,
-                                                    mask, keep_first, softcap, scale);
+                                                    mask, keep_first, softcap, scale, out_f32);
     else
       split = launch_sink_decode_any<float>(dim, vdim, heads / kv_heads, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
                                             block_tables, bt_stride, sink, gate, ldg, n_seqs, heads, kv_heads, v_heads, page, mask_kind, mask,
-                                            keep_first, softcap, scale);
+                                            keep_first, softcap, scale, out_f32);
     if (split) B2_CHECK_LAUNCH("sink_attn (one-token rows)");
   }
   const int skip = (use_mma ? 1 : 0) | (split ? 2 : 0);
   if (dtype == B2TTS_DTYPE_BF16)
     launch_sink_plain_rep<__nv_bfloat16>(heads / kv_heads, st, q, k_cache, v_cache, out, tok_seq, positions, seq_len, block_tables,
                                          bt_stride, sink, gate, ldg, n_tokens, heads, kv_heads, v_heads, dim, vdim, page, mask_kind, mask,
-                                         keep_first, softcap, scale, skip);
+                                         keep_first, softcap, scale, skip, out_f32);
   else
     launch_sink_plain_rep<float>(heads / kv_heads, st, q, k_cache, v_cache, out, tok_seq, positions, seq_len, block_tables, bt_stride,
                                  sink, gate, ldg, n_tokens, heads, kv_heads, v_heads, dim, vdim, page, mask_kind, mask, keep_first,
-                                 softcap, scale, skip);
+                                 softcap, scale, skip, out_f32);
   B2_CHECK_LAUNCH("sink_attn");
   return B2TTS_OK;
 }

@@ -151,9 +151,10 @@ class SinkSoftmaxAttention(nn.Module):
                       self.vdim, self.eps, interleaved=rot is not None and rot.interleaved, v_heads=self.v_heads)
         return q
 
-    def forward(self, q: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, q: torch.Tensor, gate: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """``out_dtype`` float32 beside bfloat16 inputs: the heads' outputs are returned unrounded."""
         lay = get_context().step_layout
-        out = torch.empty(q.shape[0], self.heads * self.vdim, dtype=q.dtype, device=q.device)
+        out = torch.empty(q.shape[0], self.heads * self.vdim, dtype=out_dtype or q.dtype, device=q.device)
         nat.sink_attn(q, self.k_cache, self.v_cache, out, lay, self.sink, gate, self.heads, self.kv_heads, self.dim, self.vdim,
                       self.k_cache.shape[1], self.mask_kind, self.mask, self.scale, v_heads=self.v_heads,
                       keep_first=self.keep_first, softcap=self.softcap)
@@ -191,6 +192,6 @@ class DifferentialAttention(SinkSoftmaxAttention):
         return self._lam
 
     def forward(self, q: torch.Tensor) -> torch.Tensor:
-        maps = super().forward(q)
+        maps = super().forward(q, out_dtype=torch.float32)       # the difference is taken before anything is rounded
         out = torch.empty(q.shape[0], self.out_heads * self.vdim, dtype=q.dtype, device=q.device)
         return nat.diff_combine(maps, out, self.lam(), 1.0 - self.diff, self.out_heads, self.vdim, self.eps)

@@ -123,6 +123,11 @@ def test_combination_of_two_attention_maps(nat, dtype, H, dv):
     nat.diff_combine(maps.reshape(9, -1).to(DEV), out, 0.37, 0.8, H, dv, 1e-4)
     want = O.rms_norm(maps[:, 0].double() - 0.37 * maps[:, 1].double(), None, 1e-4) * 0.8
     assert rel(out, want.reshape(9, -1)) < TOL[dtype]
+    # float maps beside an output of the activation type: nothing is rounded before the difference
+    fmaps = torch.randn(9, 2, H, dv, generator=g)
+    nat.diff_combine(fmaps.reshape(9, -1).to(DEV), out, 0.37, 0.8, H, dv, 1e-4)
+    want = O.rms_norm(fmaps[:, 0].double() - 0.37 * fmaps[:, 1].double(), None, 1e-4) * 0.8
+    assert rel(out, want.reshape(9, -1)) < (2e-6 if dtype == torch.float32 else 5e-3)
 
 
 @pytest.mark.parametrize("interleaved", [True, False])
@@ -170,7 +175,7 @@ def test_attention_preparation_interleaved_rotation_shared_values_and_query_only
 
 # ------------------------------------------------------------------------------------------------ attention
 def _attn_case(nat, H, G, d, dv, page, seqs, *, window=0, keep_first=0, softcap=0.0, sink=None, two_maps=False, dtype=torch.float32,
-               spike=None, seed=0, path=0, scale=0.3):
+               spike=None, seed=0, path=0, scale=0.3, float_out=False):
     """``seqs`` = [(cached, new)]: the first ``cached`` tokens are in the cache, the last ``new`` run now.  ``two_maps``: H
     and G count heads that each carry two maps over shared values (the kernel sees 2H query heads over 2G key heads and G
     value heads, map-major).  ``spike`` = (sequence, query position, key position, map): that key takes that query's
@@ -203,7 +208,7 @@ def _attn_case(nat, H, G, d, dv, page, seqs, *, window=0, keep_first=0, softcap=
         lay_seqs.append((c, n, si, bt))
         qs.append(q[c:].reshape(n, M * H * d)), refs.append(ref[c:].reshape(n, M * H * dv))
     lay = Lay(lay_seqs, page, max(len(s[3]) for s in lay_seqs))
-    out = torch.empty(lay.n_tokens, M * H * dv, dtype=dtype, device=DEV)
+    out = torch.empty(lay.n_tokens, M * H * dv, dtype=torch.float32 if float_out else dtype, device=DEV)
     sk = torch.zeros(M * H, device=DEV) if sink == "zero" else None
     nat.sink_attn(torch.cat(qs).to(DEV), kc.to(dtype).to(DEV), vc.to(dtype).to(DEV), out, lay, sk, None, M * H, M * G, d, dv, page,
                   nat.MASK_WINDOW, window, scale, path, v_heads=G, keep_first=keep_first, softcap=softcap)
@@ -244,6 +249,11 @@ def test_tensor_core_prompt_kernel_with_the_new_switches(nat, H, G, d, dv, two, 
     out, ref = _attn_case(nat, H, G, d, dv, 64, seqs, path=2, **kw)
     plain, _ = _attn_case(nat, H, G, d, dv, 64, seqs, path=1, **kw)
     assert rel(out, ref) < 1.5e-2 and rel(out, plain) < 1.5e-2
+    # unrounded outputs (floats beside bfloat16 inputs): every kernel of the launch, closer to the model than bfloat16 can be
+    fout, _ = _attn_case(nat, H, G, d, dv, 64, seqs, path=0, float_out=True, **kw)
+    assert fout.dtype == torch.float32 and rel(fout, ref) < 2e-3
+    fplain, _ = _attn_case(nat, H, G, d, dv, 64, seqs, path=1, float_out=True, **kw)
+    assert rel(fplain, ref) < 2e-3
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
